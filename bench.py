@@ -1,0 +1,400 @@
+"""Benchmark of the MSDA hot path (forward + zero-buffer backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload cfg2_m2f_1024_bf16] [--batch-per-gpu B]
+
+A step is one forward plus one backward of the operator over one batch of synthetic input
+(Mask2Former pixel-decoder shapes; see deformops_b200/workloads.py).  Metric: queries per
+second, fwd+bwd, whole job (all ranks).  One process per GPU; batch-sharded, no collective on
+the data path (torch.distributed is used only for the barrier and the max over ranks).
+
+Legs, all inside one run:
+  value     inputs resident in HBM, forward and backward launched through the C ABI,
+            timed with CUDA events on the launching stream around exactly K steps.
+            Consecutive steps use different input sets (3 sets rotate), so nothing a step
+            reads is left in L2 by the previous one ("inputs larger than L2").
+  roofline  per-kernel CUDA-event durations sampled inside the same timed region.
+  e2e       the same step through the public operator (registry.msda + autograd) with HOST
+            (pinned) input and output buffers; copies inside the timed region.
+  cpu_baseline  the CPU restatement of the reference's eager PyTorch path on a bounded
+            sample, rank 0 at N=1 only.
+
+``--impl reference`` times only the CPU restatement (the reference has no GPU-free binary
+to ship; its eager CPU path is Python on torch), on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import pathlib
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+METRIC = "MSDA fwd+bwd queries/sec"
+UNIT = "queries/s"
+NUM_SETS = 3  # rotating input sets
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2_m2f_1024_bf16")
+    ap.add_argument("--batch-per-gpu", type=int, default=None,
+                    help="samples per GPU (default: the workload's batch)")
+    ap.add_argument("--global-batch", type=int, default=None,
+                    help="fixed global batch split evenly over the GPUs (strong scaling)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0,
+                    help="target CPU time of the cpu_baseline sample")
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while a region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU restatement of the reference's eager path (cpu_baseline and --impl reference)
+# ------------------------------------------------------------------------------------------
+def cpu_eager_sample(workload_name: str, target_seconds: float, reps: int = 3):
+    """Time fwd+bwd of the eager restatement on single samples of the workload, float32."""
+    from deformops_b200.workloads import make_workload
+    from oracle.msda_eager_port import eager_forward_backward
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    w = make_workload(workload_name, batch=1, first_sample=0)
+    Q = w.sampling_locations.shape[1]
+    args = (w.value.float(), w.spatial_shapes, w.level_start_index, w.sampling_locations,
+            w.attention_weights.float(), w.grad_output.float())
+    t0 = time.perf_counter()
+    eager_forward_backward(*args)  # warm-up, also sizes the sample
+    first = time.perf_counter() - t0
+    reps = max(1, min(reps, int(target_seconds / max(first, 1e-3))))
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        eager_forward_backward(*args)
+        times.append(time.perf_counter() - t0)
+    best = min(times)
+    return {
+        "value": Q / best, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+        "sample": (f"1 sample of {workload_name} (Q={Q}) in float32, fwd+bwd, torch eager "
+                   f"restatement of the reference's CPU path, best of {reps} after 1 warm-up"),
+        "seconds_per_sample": best,
+    }
+
+
+def run_reference_arm(args):
+    """--impl reference: only rank 0 works; each step is one single-sample fwd+bwd on the CPU."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from deformops_b200.workloads import CONFIGS, make_workload
+    from oracle.msda_eager_port import eager_forward_backward
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    w = make_workload(args.workload, batch=1)
+    Q = w.sampling_locations.shape[1]
+    a = (w.value.float(), w.spatial_shapes, w.level_start_index, w.sampling_locations,
+         w.attention_weights.float(), w.grad_output.float())
+    steps = max(1, min(args.steps, 5))
+    warm = max(1, min(args.warmup, 1))
+    for _ in range(warm):
+        eager_forward_backward(*a)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        eager_forward_backward(*a)
+    dt = (time.perf_counter() - t0) / steps
+    value = Q / dt
+    cfg = CONFIGS[args.workload]
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "levels": cfg["levels"], "heads": cfg["heads"],
+                   "head_dim": cfg["head_dim"], "points": cfg["points"],
+                   "sample": "1 sample per step on the host CPU"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(),
+                         "kind": "port",
+                         "sample": f"{steps} steps of 1 sample (Q={Q}) float32 fwd+bwd, torch eager "
+                                   "restatement of the reference's CPU path"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    from deformops_b200._loader import load_library
+    from deformops_b200.ops import DTYPE_CODES, launch_counter
+    from deformops_b200.registry import Backend, msda
+    from deformops_b200.workloads import CONFIGS, make_workload
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    cfg = CONFIGS[args.workload]
+    if args.global_batch is not None:
+        assert args.global_batch % world == 0
+        B = args.global_batch // world
+        scaling = "strong"
+    else:
+        B = args.batch_per_gpu or cfg["batch"]
+        scaling = "weak"
+
+    shim = load_library()
+    sets = []
+    for r in range(NUM_SETS):
+        w = make_workload(args.workload, batch=B, first_sample=(rank * NUM_SETS + r) * B, seed=0)
+        host = {k: getattr(w, k).pin_memory() for k in
+                ("value", "sampling_locations", "attention_weights", "grad_output")}
+        d = {k: v.to(device, non_blocking=True) for k, v in host.items()}
+        d["shapes"] = w.spatial_shapes.to(device)
+        d["starts"] = w.level_start_index.to(device)
+        d["out"] = torch.empty(w.grad_output.shape, dtype=w.value.dtype, device=device)
+        d["grad_value"] = torch.empty_like(d["value"])
+        d["grad_loc"] = torch.empty_like(d["sampling_locations"])
+        d["grad_attn"] = torch.empty_like(d["attention_weights"])
+        sets.append((w, host, d))
+    w0 = sets[0][0]
+    Bq, S, G, D, Q, L, K = w0.dims
+    fwd_bytes, bwd_bytes = w0.algorithmic_bytes()
+    code = DTYPE_CODES[w0.value.dtype]
+    stream = torch.cuda.current_stream()
+    sptr = ctypes.c_void_p(stream.cuda_stream)
+
+    def abi_step(d, ev=None):
+        st = shim.forward(_p(d["value"]), _p(d["shapes"]), _p(d["starts"]),
+                          _p(d["sampling_locations"]), _p(d["attention_weights"]), _p(d["out"]),
+                          Bq, S, G, D, Q, L, K, code, 0, local_rank, sptr)
+        if ev:
+            ev[1].record(stream)
+        d["grad_value"].zero_()  # the compulsory "written once" clear, outside the kernel events
+        if ev:
+            ev[2].record(stream)
+        st |= shim.backward(_p(d["value"]), _p(d["shapes"]), _p(d["starts"]),
+                            _p(d["sampling_locations"]), _p(d["attention_weights"]),
+                            _p(d["grad_output"]), _p(d["grad_value"]), _p(d["grad_loc"]),
+                            _p(d["grad_attn"]), Bq, S, G, D, Q, L, K, code, 0, 0, local_rank, sptr)
+        if st != 0:
+            raise RuntimeError(shim.last_error())
+
+    # ---- value: resident inputs, K steps between one pair of events --------------------
+    for i in range(args.warmup):
+        abi_step(sets[i % NUM_SETS][2])
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        start.record(stream)
+        for i in range(args.steps):
+            abi_step(sets[i % NUM_SETS][2])
+        stop.record(stream)
+        barrier()
+    ms_total = start.elapsed_time(stop)
+    clock_summary = clocks.summary()
+
+    # ---- roofline: per-kernel durations, events around each launch, same rotation ---------
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    barrier()
+    for i in range(args.steps):
+        evs[i][0].record(stream)
+        abi_step(sets[i % NUM_SETS][2], evs[i])
+        evs[i][3].record(stream)
+    barrier()
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
+    zero_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
+    bwd_ms = statistics.mean(e[2].elapsed_time(e[3]) for e in evs)
+
+    # ---- e2e: public operator, host buffers, copies inside the timed region --------------
+    e2e = None
+    if not args.no_e2e:
+        def e2e_step(host, d, sink):
+            v = host["value"].to(device, non_blocking=True).requires_grad_(True)
+            l = host["sampling_locations"].to(device, non_blocking=True).requires_grad_(True)
+            a = host["attention_weights"].to(device, non_blocking=True).requires_grad_(True)
+            go = host["grad_output"].to(device, non_blocking=True)
+            out = msda(v, d["shapes"], d["starts"], l, a, backend=Backend.CUDA)
+            out.backward(go)
+            sink["out"].copy_(out.detach(), non_blocking=True)
+            sink["grad_value"].copy_(v.grad, non_blocking=True)
+            sink["grad_loc"].copy_(l.grad, non_blocking=True)
+            sink["grad_attn"].copy_(a.grad, non_blocking=True)
+
+        sink = {"out": torch.empty(sets[0][2]["out"].shape, dtype=w0.value.dtype).pin_memory(),
+                "grad_value": torch.empty(w0.value.shape, dtype=w0.value.dtype).pin_memory(),
+                "grad_loc": torch.empty(w0.sampling_locations.shape).pin_memory(),
+                "grad_attn": torch.empty(w0.attention_weights.shape, dtype=w0.value.dtype).pin_memory()}
+        e2e_steps = max(3, min(args.steps, 20))
+        for i in range(3):
+            e2e_step(sets[i % NUM_SETS][1], sets[i % NUM_SETS][2], sink)
+        barrier()
+        launch_counter.reset()
+        s2, t2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s2.record(stream)
+        for i in range(e2e_steps):
+            e2e_step(sets[i % NUM_SETS][1], sets[i % NUM_SETS][2], sink)
+        t2.record(stream)
+        barrier()
+        e2e_ms = s2.elapsed_time(t2) / e2e_steps
+        h2d = sum(h.numel() * h.element_size() for h in sets[0][1].values())
+        d2h = sum(t.numel() * t.element_size() for t in sink.values())
+        e2e = {"ms": e2e_ms, "h2d": h2d, "d2h": d2h, "steps": e2e_steps}
+
+    # ---- max over ranks -------------------------------------------------------------------
+    stats = torch.tensor([ms_total, fwd_ms, bwd_ms, zero_ms, e2e["ms"] if e2e else 0.0],
+                         device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    ms_total, fwd_ms, bwd_ms, zero_ms, e2e_ms = stats.tolist()
+
+    if rank == 0:
+        ms_per_step = ms_total / args.steps
+        queries = world * Bq * Q
+        peaks_file = ROOT / "MEASURED_PEAKS.json"
+        if peaks_file.exists():
+            peak, peak_kind = json.loads(peaks_file.read_text())["hbm_gbs"], "measured (MEASURED_PEAKS.json hbm_gbs)"
+        else:
+            peak, peak_kind = 6650.0, "fallback"
+        traffic = None
+        tfile = ROOT / "profiles" / "dram_traffic.json"
+        if tfile.exists():
+            entry = json.loads(tfile.read_text()).get("msda_backward", {})
+            per_query = entry.get("dram_bytes_per_query")
+            if per_query:
+                traffic = per_query * Bq * Q
+        achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": queries / (ms_per_step * 1e-3), "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
+            "vs_baseline": None, "dtype": {0: "f32", 1: "f16", 2: "bf16"}[code],
+            "data": "synthetic",
+            "config": {"workload": args.workload, "batch_per_gpu": Bq, "queries": Q,
+                       "levels": cfg["levels"], "heads": G, "head_dim": D, "points": K,
+                       "l2": f"{NUM_SETS} input sets rotate between steps (each step touches "
+                             f"{(fwd_bytes + bwd_bytes) / 1e6:.0f} MB, L2 is 126 MB); no flush",
+                       "parallelism": f"batch-sharded x{world}, no collective"},
+            "clocks": clock_summary,
+            "gpu_launches": 2 * args.steps,
+            "kernels_ms": {"forward": fwd_ms, "backward": bwd_ms, "grad_value_clear": zero_ms},
+            "roofline": {"bound": "hbm", "kernel": "msda backward", "achieved": achieved,
+                         "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": peak_kind, "traffic": traffic,
+                         "algorithmic_bytes": bwd_bytes,
+                         "forward": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
+                                     "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak,
+                                     "algorithmic_bytes": fwd_bytes},
+                         "fwd_bwd_vs_8TBs": (fwd_bytes + bwd_bytes) / ((fwd_ms + bwd_ms + zero_ms) * 1e-3) / 8e12},
+        }
+        if e2e:
+            line["e2e"] = {"value": queries / (e2e_ms * 1e-3), "unit": UNIT,
+                           "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                           "ms_per_step": e2e_ms, "steps": e2e["steps"],
+                           "api": "deformops_b200.registry.msda + autograd, pinned host buffers"}
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_eager_sample(args.workload, args.cpu_seconds)
+        print(json.dumps(line), flush=True)
+
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

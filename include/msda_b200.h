@@ -1,0 +1,109 @@
+/*
+ * msda_b200.h - C ABI of the sm_100a multi-scale deformable attention kernels.
+ *
+ * Plain pointers and sizes only; no torch types cross this boundary.  The library
+ * (libmsda_b200.so) is what an operator registry binds in place of the reference's
+ * native entry points.  Each function below names the reference interface it replaces
+ * (paths relative to the reference project).
+ *
+ * Conventions
+ *   - All pointers are DEVICE pointers on `device`, 16-byte aligned, contiguous row-major:
+ *       value / grad_value   (B, S, G, D)          element type `dtype`
+ *       spatial_shapes       (L, 2) int64 rows (height, width)
+ *       level_start_index    (L)    int64 exclusive prefix sum of height*width
+ *       loc / grad_loc       (B, Q, G, L, K, 2)    float32, (x, y) normalised to [0, 1]
+ *       attn / grad_attn     (B, Q, G, L*K)        element type `dtype`
+ *       out / grad_out       (B, Q, G*D)           element type `dtype`
+ *   - The level tables are read on the device; no call synchronises with the host.
+ *   - Work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = default
+ *     stream) and the call returns immediately.  Inputs are borrowed, outputs are
+ *     caller-allocated; nothing is allocated or freed here.
+ *   - Return value: MSDA_B200_OK or a negative status; the message of the last failure
+ *     on the calling thread is available from msda_b200_last_error().  No exception or
+ *     longjmp ever crosses the boundary.
+ *   - Thread safety: no mutable global state; concurrent calls from several host
+ *     threads (for example the autograd thread) are allowed.
+ *   - Supported: dtype f32 / f16 / bf16; D a multiple of 4 (f32) or 8 (f16, bf16);
+ *     1 <= L <= 16; any K >= 1 (K = 4 and K = 8 have unrolled instantiations);
+ *     S < 2^31.  B == 0 or Q == 0 is a successful no-op (backward still clears
+ *     grad_value).
+ */
+#ifndef MSDA_B200_H_
+#define MSDA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MSDA_B200_ABI_VERSION 1
+
+enum msda_b200_dtype { MSDA_B200_F32 = 0, MSDA_B200_F16 = 1, MSDA_B200_BF16 = 2 };
+
+enum msda_b200_status {
+    MSDA_B200_OK = 0,
+    MSDA_B200_INVALID_ARGUMENT = -1, /* null / misaligned pointer, negative size, bad enum */
+    MSDA_B200_UNSUPPORTED = -2,      /* shape outside the envelope listed above */
+    MSDA_B200_CUDA_ERROR = -3        /* the CUDA runtime reported an error (message has it) */
+};
+
+/* Version of this ABI; bumped on any signature change. */
+int msda_b200_abi_version(void);
+
+/* Message of the last failing call on this thread ("" if none). Never NULL. */
+const char *msda_b200_last_error(void);
+
+/*
+ * Forward: out[b,q,g,:] = sum_{l,k} a[b,q,g,l,k] * bilinear(value level l, loc[b,q,g,l,k]).
+ * apply_softmax != 0 normalises attn over its L*K entries inside the kernel first.
+ *
+ * Replaces: boxed op `<prefix>_forward` / `<prefix>_softmax_forward`
+ *   sources/deformops/backends/cuda/include/msda_boxed.cuh:14-28
+ *   sources/deformops/backends/cuda/include/msda_launch.cuh:63-138 (forward_cuda)
+ *   schema sources/deformops/backends/cuda/_schema.py:18-23
+ * Differences: the output is caller-allocated and need not be zeroed (every element is
+ * written); there is no batch chunking (chunk_step has no effect on results).
+ */
+int msda_b200_forward(const void *value, const int64_t *spatial_shapes,
+                      const int64_t *level_start_index, const float *loc, const void *attn,
+                      void *out, int64_t B, int64_t S, int64_t G, int64_t D, int64_t Q, int64_t L,
+                      int64_t K, int dtype, int apply_softmax, int device, void *stream);
+
+/*
+ * Backward: given grad_out, produces grad_value (scatter with packed 16-byte reductions),
+ * grad_loc (float32) and grad_attn (`dtype`; gradient w.r.t. the raw logits when
+ * apply_softmax != 0).  grad_loc and grad_attn are written in full (skipped points get
+ * exact zeros).  If zero_grad_value != 0 the call first clears grad_value on `stream`;
+ * pass 0 to accumulate into a buffer the caller prepared.
+ *
+ * Replaces: boxed op `<prefix>_backward` / `<prefix>_softmax_backward`
+ *   sources/deformops/backends/cuda/include/msda_boxed.cuh:32-53
+ *   sources/deformops/backends/cuda/include/msda_launch.cuh:141-275 (backward_cuda)
+ *   schema sources/deformops/backends/cuda/_schema.py:24-29
+ * Differences: gradients are caller-allocated; grad_value and grad_attn are produced
+ * directly in `dtype` (no float32 scratch copy and cast-back pass).
+ */
+int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
+                       const int64_t *level_start_index, const float *loc, const void *attn,
+                       const void *grad_out, void *grad_value, float *grad_loc, void *grad_attn,
+                       int64_t B, int64_t S, int64_t G, int64_t D, int64_t Q, int64_t L,
+                       int64_t K, int dtype, int apply_softmax, int zero_grad_value, int device,
+                       void *stream);
+
+/*
+ * Launch geometry the library would use for a shape, for harnesses that count launches
+ * or size grids: number of CTAs, queries per CTA tile and dynamic shared memory of the
+ * forward (*_fwd) and backward (*_bwd) kernels.  Pure function of its arguments.
+ * Replaces: forward_thread_layout / backward_thread_layout
+ *   sources/deformops/core/tuning.py:55-133, include/msda_launch.cuh:26-52
+ */
+int msda_b200_launch_geometry(int64_t B, int64_t G, int64_t D, int64_t Q, int64_t L, int64_t K,
+                              int dtype, int apply_softmax, int64_t *grid, int *tile_queries,
+                              int64_t *smem_fwd, int64_t *smem_bwd);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MSDA_B200_H_ */

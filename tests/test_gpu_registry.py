@@ -1,0 +1,177 @@
+"""GPU tests of the operator surface: functional, autograd, custom ops, operand hygiene."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import msda_oracle as orc
+from tests._abi import abi_backward, abi_forward, dev, to_np
+from tests._golden import load, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(name="small_b", dtype=torch.float32):
+    c = load(name)
+    t = {k: dev(c[k], dtype) for k in ("value", "loc", "attn_linear", "attn_logits", "grad_out")}
+    t["loc"] = dev(c["loc"], torch.float32)
+    t["shapes"], t["starts"] = dev(c["spatial_shapes"]), dev(c["level_start_index"])
+    return c, t
+
+
+@pytest.mark.parametrize("method", ["linear", "softmax"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_functional_autograd_equals_abi(method, dtype):
+    from deformops_b200.registry import Backend, msda
+
+    _, t = _case(dtype=dtype)
+    attn = t["attn_logits"] if method == "softmax" else t["attn_linear"]
+    v, l, a = (x.clone().requires_grad_(True) for x in (t["value"], t["loc"], attn))
+    out = msda(v, t["shapes"], t["starts"], l, a, method=method, backend=Backend.CUDA)
+    out.backward(t["grad_out"])
+    e_out = abi_forward(t["value"], t["shapes"], t["starts"], t["loc"], attn, softmax=method == "softmax")
+    e_gv, e_gl, e_ga = abi_backward(t["value"], t["shapes"], t["starts"], t["loc"], attn,
+                                    t["grad_out"], softmax=method == "softmax")
+    assert torch.equal(out, e_out)
+    assert torch.equal(l.grad, e_gl) and torch.equal(a.grad, e_ga)
+    tol = 1e-6 if dtype == torch.float32 else 2e-2  # atomics reorder grad_value sums
+    torch.testing.assert_close(v.grad, e_gv, rtol=tol, atol=tol)
+    assert v.grad.dtype == dtype and l.grad.dtype == torch.float32 and a.grad.dtype == dtype
+
+
+def test_non_contiguous_split_weights_int32_tables_and_16bit_locations():
+    """Any memory layout, (B,Q,G,L,K) weights, int32 level tables, low-precision locations."""
+    from deformops_b200.registry import msda
+
+    c, t = _case("small_b")
+    B, Q, G, L, K, _ = c["loc"].shape
+    value = t["value"].transpose(1, 2).contiguous().transpose(1, 2)      # strided view
+    loc = t["loc"].flip(-1).contiguous().flip(-1)
+    attn5 = t["attn_linear"].view(B, Q, G, L, K)
+    v, l, a = (x.detach().requires_grad_(True) for x in (value, loc, attn5))
+    assert not v.is_contiguous() and not l.is_contiguous()
+    out = msda(v, t["shapes"].int(), t["starts"].int(), l, a)
+    out.backward(t["grad_out"])
+    assert rel_err(to_np(out), c["linear_out_eager"]) < 1e-5
+    assert a.grad.shape == attn5.shape
+    assert rel_err(to_np(a.grad).reshape(B, Q, G, L * K), c["linear_grad_attn"]) < 1e-4
+    assert rel_err(to_np(v.grad), c["linear_grad_value"]) < 1e-4
+    assert rel_err(to_np(l.grad), c["linear_grad_loc"]) < 1e-4
+
+    # bf16 locations are widened to float32 before the kernel; the gradient returns as bf16
+    lb = t["loc"].bfloat16().requires_grad_(True)
+    vb = t["value"].bfloat16()
+    ab = t["attn_linear"].bfloat16()
+    ob = msda(vb, t["shapes"], t["starts"], lb, ab)
+    ob.float().sum().backward()
+    assert lb.grad.dtype == torch.bfloat16
+    e = orc.forward(vb.cpu(), c["spatial_shapes"], c["level_start_index"], lb.detach().cpu(), ab.cpu())
+    assert rel_err(to_np(ob), e) < 1e-2
+
+
+def test_public_ops_no_grad_inference_and_vmap():
+    from deformops_b200.registry import msda
+
+    c, t = _case("small_b")
+    args = (t["value"], t["shapes"], t["starts"], t["loc"], t["attn_linear"])
+    ref = msda(*args)
+    with torch.no_grad():
+        assert torch.equal(torch.ops.deformops_b200.msda(*args), ref)
+    with torch.inference_mode():
+        assert torch.equal(torch.ops.deformops_b200.msda(*args), ref)
+    sm = torch.ops.deformops_b200.msda_softmax(t["value"], t["shapes"], t["starts"], t["loc"],
+                                               t["attn_logits"])
+    assert rel_err(to_np(sm), c["softmax_out_eager"]) < 1e-5
+    # vmap over an extra leading axis folds into the batch: one kernel run, same numbers
+    stacked = [torch.stack([x, x * 1.0]) for x in (t["value"], t["loc"], t["attn_linear"])]
+    out = torch.vmap(torch.ops.deformops_b200.msda, in_dims=(0, None, None, 0, 0))(
+        stacked[0], t["shapes"], t["starts"], stacked[1], stacked[2])
+    assert out.shape == (2, *ref.shape)
+    assert torch.equal(out[0], ref) and torch.equal(out[1], ref)
+    with pytest.raises(ValueError, match="shared"):
+        torch.vmap(torch.ops.deformops_b200.msda, in_dims=(0, 0, None, 0, 0))(
+            stacked[0], torch.stack([t["shapes"]] * 2), t["starts"], stacked[1], stacked[2])
+
+
+def test_opcheck_private_and_public_ops():
+    _, t = _case("small_a")
+    K = t["loc"].shape[4]
+    v, l, a = (x.clone().requires_grad_(True) for x in (t["value"], t["loc"], t["attn_linear"]))
+    torch.library.opcheck(torch.ops.deformops_b200.msda_forward.default,
+                          (v, t["shapes"], t["starts"], l, a, 128, K, 0, 0))
+    torch.library.opcheck(torch.ops.deformops_b200.msda_softmax_forward.default,
+                          (v, t["shapes"], t["starts"], l, a, 128, K, 0, 0))
+    torch.library.opcheck(torch.ops.deformops_b200.msda_backward.default,
+                          (t["value"], t["shapes"], t["starts"], t["loc"], t["attn_linear"],
+                           t["grad_out"], 128, K, 0, 0),
+                          test_utils=("test_schema", "test_faketensor"))
+    torch.library.opcheck(torch.ops.deformops_b200.msda.default,
+                          (v, t["shapes"], t["starts"], l, a),
+                          test_utils=("test_schema", "test_faketensor", "test_aot_dispatch_static"))
+
+
+def test_fake_tensor_backward_and_compile():
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    from deformops_b200.registry import msda
+
+    c, t = _case("small_b")
+    with FakeTensorMode(allow_non_fake_inputs=False) as mode:
+        f = {k: mode.from_tensor(x) for k, x in t.items()}
+        v, l, a = (f[k].clone().requires_grad_(True) for k in ("value", "loc", "attn_linear"))
+        out = torch.ops.deformops_b200.msda(v, f["shapes"], f["starts"], l, a)
+        out.sum().backward()
+        assert v.grad.shape == v.shape and l.grad.shape == l.shape and a.grad.shape == a.shape
+
+    compiled = torch.compile(lambda *xs: msda(*xs), backend="aot_eager", fullgraph=True)
+    args = (t["value"], t["shapes"], t["starts"], t["loc"], t["attn_linear"])
+    assert torch.equal(compiled(*args), msda(*args))
+
+
+def test_errors_before_launch():
+    from deformops_b200.registry import Backend, NoBackendError, msda  # type: ignore[attr-defined]
+
+    _, t = _case("small_b")
+    args = [t["value"], t["shapes"], t["starts"], t["loc"], t["attn_linear"]]
+    with pytest.raises(TypeError):
+        msda(*args, backend="cuda")
+    with pytest.raises(TypeError):
+        msda(*args, bogus=1)
+    with pytest.raises(TypeError):
+        msda(args[0], args[1])
+    with pytest.raises(ValueError):
+        msda(args[0], args[1], args[2], args[3][:, :, :1], args[4])
+    with pytest.raises(ValueError):
+        msda(args[0], args[1], args[2], args[3], args[4].double())
+    with pytest.raises(NoBackendError):
+        msda(*args, backend=Backend.TRITON)
+    with pytest.raises(NoBackendError):
+        msda(*[a.double() if a.is_floating_point() else a for a in args])
+    with pytest.raises(NoBackendError):
+        msda(*[a.cpu() for a in args])
+
+
+def test_empty_calls_return_zeros_without_launch():
+    from deformops_b200.ops import launch_counter
+    from deformops_b200.registry import msda
+
+    _, t = _case("small_b")
+    launch_counter.reset()
+    out = msda(t["value"], t["shapes"], t["starts"], t["loc"][:, :0], t["attn_linear"][:, :0])
+    assert out.shape == (t["value"].shape[0], 0, t["value"].shape[2] * t["value"].shape[3])
+    out = msda(t["value"][:0], t["shapes"], t["starts"], t["loc"][:0], t["attn_linear"][:0])
+    assert out.numel() == 0 and launch_counter.kernels == 0
+
+
+def test_autocast_keeps_float32_locations():
+    from deformops_b200.registry import msda
+
+    c, t = _case("small_b", torch.bfloat16)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = msda(t["value"], t["shapes"], t["starts"], t["loc"], t["attn_linear"])
+    assert out.dtype == torch.bfloat16
+    e = orc.forward(t["value"].cpu(), c["spatial_shapes"], c["level_start_index"], t["loc"].cpu(),
+                    t["attn_linear"].cpu())
+    assert rel_err(to_np(out), e) < 1e-2

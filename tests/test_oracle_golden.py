@@ -90,3 +90,24 @@ def test_oracle_cfg0_matches_reference(method):
         assert rel_err(rows, gold[f"{method}_{key}_rows"]) < 1e-12, key
         assert float(arr.sum()) == pytest.approx(float(gold[f"{method}_{key}_sum"]), rel=1e-9, abs=1e-7)
         assert float(np.abs(arr).sum()) == pytest.approx(float(gold[f"{method}_{key}_abssum"]), rel=1e-10)
+
+
+@pytest.mark.parametrize("method", METHODS)
+@pytest.mark.parametrize("name", ["boundary", "small_b", "small_c", "ragged", "all_outside"])
+def test_eager_port_matches_reference(name, method):
+    """The torch restatement of the reference's eager path (timed as the CPU baseline)."""
+    import torch
+
+    from oracle.msda_eager_port import eager_forward_backward
+
+    case = load(name)
+    t = {k: torch.from_numpy(case[k]).double() for k in ("value", "loc", "grad_out")}
+    attn = torch.from_numpy(attn_for(case, method)).double()
+    out, gv, gl, ga = eager_forward_backward(
+        t["value"], torch.from_numpy(case["spatial_shapes"]),
+        torch.from_numpy(case["level_start_index"]), t["loc"], attn, t["grad_out"],
+        softmax=method == "softmax")
+    assert rel_err(out.numpy(), case[f"{method}_out_eager"]) < 1e-12
+    assert rel_err(gv.numpy(), case[f"{method}_grad_value"]) < 1e-12
+    assert rel_err(gl.numpy(), case[f"{method}_grad_loc"]) < 1e-12
+    assert rel_err(ga.numpy(), case[f"{method}_grad_attn"]) < 1e-12
