@@ -19,7 +19,7 @@ from .core.errors import KernelBuildError, KernelUnavailableError
 
 __all__ = ["ABI_VERSION", "Shim", "library_path", "load_library", "loaded"]
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 _lock = threading.Lock()
 _shim: "Shim | None" = None
@@ -40,7 +40,8 @@ class Shim:
 
     #: every symbol ``include/msda_b200.h`` declares
     SYMBOLS = ("msda_b200_abi_version", "msda_b200_last_error", "msda_b200_forward",
-               "msda_b200_backward", "msda_b200_launch_geometry")
+               "msda_b200_backward", "msda_b200_backward_scratch_bytes",
+               "msda_b200_launch_geometry")
 
     def __init__(self, path: str):
         self.path = path
@@ -57,7 +58,11 @@ class Shim:
         self.forward.argtypes = [_vp] * 6 + [_i64] * 7 + [_int, _int, _int, _vp]
         self.backward = self.lib.msda_b200_backward
         self.backward.restype = _int
-        self.backward.argtypes = [_vp] * 9 + [_i64] * 7 + [_int, _int, _int, _int, _vp]
+        self.backward.argtypes = ([_vp] * 10 + [_i64, _i64] + [_i64] * 7
+                                  + [_int, _int, _int, _int, _vp])
+        self.scratch_bytes = self.lib.msda_b200_backward_scratch_bytes
+        self.scratch_bytes.restype = _i64
+        self.scratch_bytes.argtypes = [_i64] * 4 + [_int]
         self.launch_geometry = self.lib.msda_b200_launch_geometry
         self.launch_geometry.restype = _int
         self.launch_geometry.argtypes = [_i64] * 6 + [_int, _int, ctypes.POINTER(_i64),

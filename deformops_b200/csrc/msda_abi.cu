@@ -23,9 +23,11 @@ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 int element_size(int dtype) { return dtype == MSDA_B200_F32 ? 4 : 2; }
 
+constexpr size_t kSmemBudget = 96 * 1024;   // per CTA, so that at least two CTAs share an SM
+
 // Shape checks shared by forward, backward and the geometry query; fills the launch plan.
 int plan(msda_b200::Params &p, int64_t B, int64_t S, int64_t G, int64_t D, int64_t Q, int64_t L,
-         int64_t K, int dtype, bool softmax, bool backward) {
+         int64_t K, int dtype, bool softmax) {
     if (dtype != MSDA_B200_F32 && dtype != MSDA_B200_F16 && dtype != MSDA_B200_BF16)
         return fail(MSDA_B200_INVALID_ARGUMENT, "dtype %d is not f32(0), f16(1) or bf16(2)", dtype);
     if (B < 0 || S < 0 || Q < 0 || G <= 0 || D <= 0 || L <= 0 || K <= 0)
@@ -43,8 +45,11 @@ int plan(msda_b200::Params &p, int64_t B, int64_t S, int64_t G, int64_t D, int64
     if (L > msda_b200::kMaxLevels)
         return fail(MSDA_B200_UNSUPPORTED, "L=%lld levels exceed the supported %d", (long long)L,
                     msda_b200::kMaxLevels);
-    if (S >= (int64_t)1 << 31 || G * D >= (int64_t)1 << 24 || L * K >= (int64_t)1 << 16)
-        return fail(MSDA_B200_UNSUPPORTED, "S, G*D or L*K too large for 32-bit tile indexing");
+    if (S * G * D >= (int64_t)1 << 31 || L * K >= (int64_t)1 << 15)
+        return fail(MSDA_B200_UNSUPPORTED,
+                    "S*G*D = %lld must stay below 2^31 (32-bit offsets inside a sample) and "
+                    "L*K below 2^15",
+                    (long long)(S * G * D));
 
     p.B = B;
     p.S = S;
@@ -53,30 +58,30 @@ int plan(msda_b200::Params &p, int64_t B, int64_t S, int64_t G, int64_t D, int64
     p.D = (int)D;
     p.L = (int)L;
     p.K = (int)K;
-    int lanes = (int)(D / vec), lg = 0;
+    const int lanes = (int)(D / vec);
+    int lg = 0;
     while ((1 << lg) < lanes && lg < 5) ++lg;
     p.lph_log2 = lg;
+    const int ppw = 32 >> lg;
+    const int P = (int)(L * K);
+    p.point_chunk = P < msda_b200::kDescPerWarp / ppw ? P : msda_b200::kDescPerWarp / ppw;
+    if (lanes > 32 && P > p.point_chunk)
+        return fail(MSDA_B200_UNSUPPORTED,
+                    "D=%lld needs several channel passes and L*K=%d several point chunks; "
+                    "only one of the two is supported",
+                    (long long)D, P);
 
-    // queries per CTA tile: a multiple of 8 keeps every tile's loc/attn slice 16-byte
-    // aligned; prefer the largest tile that still lets four CTAs share an SM
-    const int64_t per_query = G * L * K * (int64_t)sizeof(float) * ((backward && softmax) ? 4 : 3);
-    int tq = 0;
-    for (int cand : {32, 24, 16, 8})
-        if (cand * per_query <= 56 * 1024) {
-            tq = cand;
-            break;
-        }
-    if (tq == 0) {
-        if (8 * per_query > 200 * 1024)
-            return fail(MSDA_B200_UNSUPPORTED,
-                        "G*L*K = %lld does not fit a shared-memory tile of 8 queries",
-                        (long long)(G * L * K));
-        tq = 8;
-    }
-    p.tile_queries = tq;
-    p.num_tiles = (B * Q + tq - 1) / tq;
-    if (p.num_tiles >= (int64_t)1 << 31)
-        return fail(MSDA_B200_UNSUPPORTED, "B*Q = %lld needs too many CTAs", (long long)(B * Q));
+    // CTA size: 8 warps unless the per-warp gradient staging of the backward is too large
+    p.threads = 256;
+    while (p.threads > 32 && (msda_b200::backward_smem_bytes(p, softmax) > kSmemBudget ||
+                              msda_b200::forward_smem_bytes(p, softmax) > kSmemBudget))
+        p.threads >>= 1;
+    if (msda_b200::backward_smem_bytes(p, softmax) > 200 * 1024)
+        return fail(MSDA_B200_UNSUPPORTED, "L*K = %d is too large for the shared-memory staging", P);
+    const int nwarps = p.threads / 32;
+    p.num_groups = (B * Q * G + ppw - 1) / ppw;
+    const int64_t grid = (p.num_groups + nwarps - 1) / nwarps;
+    p.grid = (unsigned)(grid > 0x7fffffff ? 0x7fffffff : grid);   // kernels are grid-stride
     return MSDA_B200_OK;
 }
 
@@ -111,18 +116,22 @@ int msda_b200_abi_version(void) { return MSDA_B200_ABI_VERSION; }
 
 const char *msda_b200_last_error(void) { return g_error; }
 
+int64_t msda_b200_backward_scratch_bytes(int64_t B, int64_t S, int64_t G, int64_t D, int dtype) {
+    if (dtype != MSDA_B200_F16 && dtype != MSDA_B200_BF16) return 0;
+    if (B <= 0 || S <= 0 || G <= 0 || D <= 0) return 0;
+    return B * S * G * D * (int64_t)sizeof(float);
+}
+
 int msda_b200_launch_geometry(int64_t B, int64_t G, int64_t D, int64_t Q, int64_t L, int64_t K,
-                              int dtype, int apply_softmax, int64_t *grid, int *tile_queries,
+                              int dtype, int apply_softmax, int64_t *grid, int *threads,
                               int64_t *smem_fwd, int64_t *smem_bwd) {
-    msda_b200::Params pf{}, pb{};
-    int st = plan(pf, B, 1, G, D, Q, L, K, dtype, apply_softmax != 0, false);
+    msda_b200::Params p{};
+    const int st = plan(p, B, 1, G, D, Q, L, K, dtype, apply_softmax != 0);
     if (st != MSDA_B200_OK) return st;
-    st = plan(pb, B, 1, G, D, Q, L, K, dtype, apply_softmax != 0, true);
-    if (st != MSDA_B200_OK) return st;
-    if (grid) *grid = pf.num_tiles;
-    if (tile_queries) *tile_queries = pf.tile_queries;
-    if (smem_fwd) *smem_fwd = (int64_t)msda_b200::forward_smem_bytes(pf);
-    if (smem_bwd) *smem_bwd = (int64_t)msda_b200::backward_smem_bytes(pb, apply_softmax != 0);
+    if (grid) *grid = p.grid;
+    if (threads) *threads = p.threads;
+    if (smem_fwd) *smem_fwd = (int64_t)msda_b200::forward_smem_bytes(p, apply_softmax != 0);
+    if (smem_bwd) *smem_bwd = (int64_t)msda_b200::backward_smem_bytes(p, apply_softmax != 0);
     return MSDA_B200_OK;
 }
 
@@ -131,7 +140,7 @@ int msda_b200_forward(const void *value, const int64_t *spatial_shapes,
                       void *out, int64_t B, int64_t S, int64_t G, int64_t D, int64_t Q, int64_t L,
                       int64_t K, int dtype, int apply_softmax, int device, void *stream) {
     msda_b200::Params p{};
-    const int st = plan(p, B, S, G, D, Q, L, K, dtype, apply_softmax != 0, false);
+    const int st = plan(p, B, S, G, D, Q, L, K, dtype, apply_softmax != 0);
     if (st != MSDA_B200_OK) return st;
     if (B == 0 || Q == 0) return MSDA_B200_OK;
     if (!value || !spatial_shapes || !level_start_index || !loc || !attn || !out)
@@ -156,29 +165,40 @@ int msda_b200_forward(const void *value, const int64_t *spatial_shapes,
 int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
                        const int64_t *level_start_index, const float *loc, const void *attn,
                        const void *grad_out, void *grad_value, float *grad_loc, void *grad_attn,
-                       int64_t B, int64_t S, int64_t G, int64_t D, int64_t Q, int64_t L,
-                       int64_t K, int dtype, int apply_softmax, int zero_grad_value, int device,
-                       void *stream) {
+                       void *scratch, int64_t scratch_bytes, int64_t scratch_adds, int64_t B,
+                       int64_t S, int64_t G, int64_t D, int64_t Q, int64_t L, int64_t K, int dtype,
+                       int apply_softmax, int zero_grad_value, int device, void *stream) {
     msda_b200::Params p{};
-    const int st = plan(p, B, S, G, D, Q, L, K, dtype, apply_softmax != 0, true);
+    const int st = plan(p, B, S, G, D, Q, L, K, dtype, apply_softmax != 0);
     if (st != MSDA_B200_OK) return st;
     if (B == 0) return MSDA_B200_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    DeviceGuard guard(device);
-    if (guard.err != cudaSuccess) return cuda_fail(guard.err, "backward: selecting the device");
-    if (zero_grad_value && S > 0) {
-        if (!grad_value) return fail(MSDA_B200_INVALID_ARGUMENT, "backward: grad_value is null");
-        const cudaError_t e = cudaMemsetAsync(
-            grad_value, 0, (size_t)(B * S * G * D) * element_size(dtype), s);
-        if (e != cudaSuccess) return cuda_fail(e, "backward: clearing grad_value");
+    const bool use_scratch = scratch != nullptr && dtype != MSDA_B200_F32 && S > 0 && Q > 0;
+    if (use_scratch) {
+        if (!zero_grad_value)
+            return fail(MSDA_B200_INVALID_ARGUMENT,
+                        "backward: accumulating into a caller-prepared grad_value "
+                        "(zero_grad_value = 0) cannot be combined with a scratch buffer");
+        const int64_t need = msda_b200_backward_scratch_bytes(B, S, G, D, dtype);
+        if (scratch_bytes < need)
+            return fail(MSDA_B200_INVALID_ARGUMENT,
+                        "backward: scratch holds %lld bytes, %lld are needed",
+                        (long long)scratch_bytes, (long long)need);
+        if (!aligned16(scratch))
+            return fail(MSDA_B200_INVALID_ARGUMENT, "backward: scratch must be 16-byte aligned");
+        if (scratch_adds < 0)
+            return fail(MSDA_B200_INVALID_ARGUMENT, "backward: scratch_adds must be >= 0");
     }
-    if (Q == 0) return MSDA_B200_OK;
-    if (!value || !spatial_shapes || !level_start_index || !loc || !attn || !grad_out ||
-        !grad_value || !grad_loc || !grad_attn)
-        return fail(MSDA_B200_INVALID_ARGUMENT, "backward: null pointer argument");
-    if (!aligned16(value) || !aligned16(loc) || !aligned16(attn) || !aligned16(grad_out) ||
-        !aligned16(grad_value) || !aligned16(grad_loc) || !aligned16(grad_attn))
-        return fail(MSDA_B200_INVALID_ARGUMENT, "backward: all tensors must be 16-byte aligned");
+    if ((S > 0 && !grad_value) || !aligned16(grad_value))
+        return fail(MSDA_B200_INVALID_ARGUMENT, "backward: grad_value is null or misaligned");
+    if (Q > 0) {
+        if (!value || !spatial_shapes || !level_start_index || !loc || !attn || !grad_out ||
+            !grad_loc || !grad_attn)
+            return fail(MSDA_B200_INVALID_ARGUMENT, "backward: null pointer argument");
+        if (!aligned16(value) || !aligned16(loc) || !aligned16(attn) || !aligned16(grad_out) ||
+            !aligned16(grad_loc) || !aligned16(grad_attn))
+            return fail(MSDA_B200_INVALID_ARGUMENT, "backward: all tensors must be 16-byte aligned");
+    }
     p.value = value;
     p.spatial_shapes = spatial_shapes;
     p.level_start_index = level_start_index;
@@ -188,8 +208,26 @@ int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
     p.grad_value = grad_value;
     p.grad_loc = grad_loc;
     p.grad_attn = grad_attn;
-    const cudaError_t e = msda_b200::launch_backward(p, dtype, apply_softmax != 0, s);
+    p.scratch = use_scratch ? static_cast<float *>(scratch) : nullptr;
+    p.scratch_adds = scratch_adds > 0 ? scratch_adds : (dtype == MSDA_B200_BF16 ? 32 : 512);
+
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return cuda_fail(guard.err, "backward: selecting the device");
+    cudaError_t e;
+    if (use_scratch) {
+        e = msda_b200::launch_prepare_grad_value(p, dtype, s);
+        if (e != cudaSuccess) return cuda_fail(e, "backward: clearing grad_value / scratch");
+    } else if (zero_grad_value && S > 0) {
+        e = cudaMemsetAsync(grad_value, 0, (size_t)(B * S * G * D) * element_size(dtype), s);
+        if (e != cudaSuccess) return cuda_fail(e, "backward: clearing grad_value");
+    }
+    if (Q == 0) return MSDA_B200_OK;
+    e = msda_b200::launch_backward(p, dtype, apply_softmax != 0, s);
     if (e != cudaSuccess) return cuda_fail(e, "backward: kernel launch");
+    if (use_scratch) {
+        e = msda_b200::launch_finalize_grad_value(p, dtype, s);
+        if (e != cudaSuccess) return cuda_fail(e, "backward: converting the scratch levels");
+    }
     return MSDA_B200_OK;
 }
 

@@ -1,230 +1,342 @@
-// Backward kernel: scatters grad_value and reduces grad_loc / grad_attn with no
+// Backward kernels: scatter grad_value and reduce grad_loc / grad_attn with no
 // intermediate sampling buffer in global memory.
 //
 // Replaces the reference's backward path
 //   sources/deformops/backends/cuda/include/msda_backward.cuh:14-240 (kernel)
 //   sources/deformops/backends/cuda/include/interpolate.cuh:78-218   (scatter + gradients)
 //   sources/deformops/backends/cuda/include/utils.cuh:172-220         (softmax Jacobian, reductions)
-// with a design of its own:
-//  * the tile's locations and weights are staged in shared memory once (coalesced,
-//    streaming); the same shared tile later carries grad_loc / grad_attn, which leave
-//    the CTA as coalesced 16-byte streaming stores;
-//  * every lane owns 16 bytes of channels, reloads the four corners with one 16-byte
-//    load each, and issues ONE 16-byte packed reduction per corner
-//    (red.global.add.noftz.v4.bf16x2 / .v4.f16x2 / .v4.f32) into grad_value - lanes of
-//    a warp instruction always target distinct (pixel, head, channel-group) addresses;
-//  * the three per-point scalars (d/dx, d/dy, d/da) come from four corner dot products
-//    and are reduced over the LPH lanes of a slot with xor shuffles;
-//  * softmax weights are normalised in shared memory and the softmax Jacobian is applied
-//    as p_i * (g_i - sum_j p_j g_j), one thread per (query, head) pair.
+//   sources/deformops/backends/cuda/include/msda_launch.cuh:188-197,252-273 (scratch, cast-back)
+// with a design of its own.  A warp owns a group of 32/LPH (query, head) pairs:
+//  * pre-pass as in the forward kernel: one lane per point builds a 32-byte descriptor
+//    (corner offset, row stride, flags, weight a, fractions, a*W, a*H) in shared memory;
+//  * every lane owns 16 bytes of channels, reloads the four corners (predicated 16-byte
+//    loads), forms four corner dot products with grad_out and issues ONE 16-byte packed
+//    reduction per corner into grad_value (red.global.add.noftz.v4.bf16x2 / .v4.f16x2 /
+//    .v4.f32); lanes of one warp instruction always target distinct addresses;
+//  * d/dx, d/dy, d/da follow from the four dots and are reduced over the slot's lanes with
+//    xor shuffles; they are staged in shared memory and leave the warp as contiguous
+//    streaming stores (grad_loc float32, grad_attn in T);
+//  * softmax: weights are normalised in the pre-pass and the Jacobian is applied as
+//    p_i * (g_i - sum_j p_j g_j) before the store.
+//
+// Accuracy of 16-bit grad_value.  A coarse pyramid level receives hundreds of additions
+// per element; summing those in bf16 loses about sqrt(n) * 2^-9 of the result.  Levels
+// whose expected additions per element, 4*K*Q / (H*W), exceed `scratch_adds` therefore
+// accumulate in a float32 scratch with red.global.add.v4.f32 and are converted once by
+// finalize_kernel; the fine levels, which hold most of the bytes, keep the direct packed
+// 16-bit reductions.  prepare_kernel clears exactly the rows each path adds into.
 #include "msda_common.cuh"
 
 namespace msda_b200 {
 
 namespace {
 
-template <typename T, int KT, bool SOFTMAX>
-__global__ void __launch_bounds__(kThreads, 3) backward_kernel(const Params p) {
+// predicated packed reductions: one instruction, no branch
+template <typename T>
+__device__ __forceinline__ void red_if(T *addr, const float2 (&g)[VecTraits<T>::kVec / 2], bool pred);
+
+template <>
+__device__ __forceinline__ void red_if<float>(float *addr, const float2 (&g)[2], bool pred) {
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %5, 0;\n\t"
+                 "@q red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n\t}" ::"l"(addr),
+                 "f"(g[0].x), "f"(g[0].y), "f"(g[1].x), "f"(g[1].y), "r"((unsigned)pred));
+}
+template <>
+__device__ __forceinline__ void red_if<__nv_bfloat16>(__nv_bfloat16 *addr, const float2 (&g)[4],
+                                                      bool pred) {
+    const uint4 v = VecTraits<__nv_bfloat16>::pack(g);
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %5, 0;\n\t"
+                 "@q red.relaxed.gpu.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};\n\t}" ::"l"(
+                     addr),
+                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"((unsigned)pred));
+}
+template <>
+__device__ __forceinline__ void red_if<__half>(__half *addr, const float2 (&g)[4], bool pred) {
+    const uint4 v = VecTraits<__half>::pack(g);
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %5, 0;\n\t"
+                 "@q red.relaxed.gpu.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};\n\t}" ::"l"(
+                     addr),
+                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"((unsigned)pred));
+}
+
+template <typename T, bool SOFTMAX>
+__global__ void __launch_bounds__(256, 3) backward_kernel(const Params p) {
     using VT = VecTraits<T>;
     constexpr int V = VT::kVec;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int NV2 = V / 2;
+    extern __shared__ uint4 smem[];
     __shared__ LevelTable lt;
 
-    const int G = p.G, D = p.D, L = p.L;
-    const int K = KT > 0 ? KT : p.K;
-    const int P = L * K;
-    const int TQ = p.tile_queries;
-    float *sLoc = reinterpret_cast<float *>(smem_raw);   // in: loc, out: grad_loc   [pair][P][2]
-    float *sAttn = sLoc + (size_t)TQ * G * P * 2;         // weights / probabilities [pair][P]
-    // gradient w.r.t. the (normalised) weights; aliases sAttn when there is no softmax
-    float *sGrad = SOFTMAX ? sAttn + (size_t)TQ * G * P : sAttn;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nwarps = blockDim.x >> 5;
+    const int lph = 1 << p.lph_log2;
+    const int ppw = 32 >> p.lph_log2;
+    const int PC = p.point_chunk;
+    const int G = p.G, D = p.D, K = p.K;
+    const int P = p.L * K;
+    const int GD = G * D;
+    const float inv_K = 1.f / (float)K;
+    const float inv_P = 1.f / (float)P;
+
+    // per-warp shared memory: descriptors, then staged gradients of the whole group
+    uint4 *desc = smem + (size_t)warp * (kDescPerWarp * 2);
+    const int stage_floats = backward_stage_floats(ppw, P, SOFTMAX);
+    float *stage = reinterpret_cast<float *>(smem + (size_t)nwarps * (kDescPerWarp * 2)) +
+                   (size_t)warp * stage_floats;
+    float2 *s_stats = reinterpret_cast<float2 *>(stage);         // [32] softmax (max, 1/sum)
+    float2 *s_gloc = s_stats + 32;                               // [ppw*P] (dx, dy)
+    float *s_gatt = stage + 64 + ppw * P * 2;                    // [ppw*P] d/d(weight)
+    float *s_prob = s_gatt + ppw * P;                            // [ppw*P] softmax only
 
     load_level_table(lt, p);
-
-    const int64_t total_q = p.B * p.Q;
-    const int64_t bq0 = (int64_t)blockIdx.x * TQ;
-    const int nq = (int)min((int64_t)TQ, total_q - bq0);
-    const int npairs = nq * G;
-
-    stage_f32(sLoc, p.loc + bq0 * G * P * 2, npairs * P * 2);
-    stage_as_f32<T>(sAttn, reinterpret_cast<const T *>(p.attn) + bq0 * G * P, npairs * P);
     __syncthreads();
 
-    if constexpr (SOFTMAX) {
-        for (int pair = threadIdx.x; pair < npairs; pair += kThreads) {
-            float *a = sAttn + pair * P;
-            float m = -INFINITY;
-            for (int i = 0; i < P; ++i) m = fmaxf(m, a[i]);
-            float sum = 0.f;
-            for (int i = 0; i < P; ++i) {
-                const float e = expf(a[i] - m);
-                a[i] = e;
-                sum += e;
-            }
-            const float inv = 1.f / sum;
-            for (int i = 0; i < P; ++i) a[i] *= inv;
-        }
-        __syncthreads();
-    }
-
-    const int lph = 1 << p.lph_log2;
-    const int slot = threadIdx.x >> p.lph_log2;
-    const int sub = threadIdx.x & (lph - 1);
-    const int nslots = kThreads >> p.lph_log2;
-    const int GD = G * D;
+    const int64_t total_pairs = p.B * p.Q * G;
+    const int slot = lane >> p.lph_log2;
+    const int sub = lane & (lph - 1);
     const T *value = reinterpret_cast<const T *>(p.value);
+    const T *attn = reinterpret_cast<const T *>(p.attn);
     const T *grad_out = reinterpret_cast<const T *>(p.grad_out);
+    const float2 *loc2 = reinterpret_cast<const float2 *>(p.loc);
     T *grad_value = reinterpret_cast<T *>(p.grad_value);
-    const int ch0 = sub * V;
 
-    // warp-uniform trip count: every lane takes part in the shuffles of every iteration
-    for (int base = 0; base < npairs; base += nslots) {
-        const bool live = base + slot < npairs;
-        const int pair = live ? base + slot : npairs - 1;
-        const int64_t bq = bq0 + pair / G;
-        const int g = pair % G;
-        const int64_t b = bq / p.Q;
-        float2 *pl = reinterpret_cast<float2 *>(sLoc) + pair * P;
-        const float *pa = sAttn + pair * P;
-        float *pg = sGrad + pair * P;
-        const int64_t sample_base = (b * p.S * G + g) * (int64_t)D;
-        const T *go_row = grad_out + (bq * G + g) * (int64_t)D;
-
-        float2 go0[V / 2];  // this lane's first (usually only) channel vector of grad_out
-        {
-            float f[V];
-#pragma unroll
-            for (int i = 0; i < V; ++i) f[i] = 0.f;
-            if (live && ch0 < D) VT::unpack(ld_stream16(go_row + ch0), f);
-#pragma unroll
-            for (int i = 0; i < V / 2; ++i) go0[i] = make_float2(f[2 * i], f[2 * i + 1]);
+    for (int64_t group = (int64_t)blockIdx.x * nwarps + warp; group < p.num_groups;
+         group += (int64_t)gridDim.x * nwarps) {
+        const int64_t pair0 = group * ppw;
+        const int nlive = (int)min((int64_t)ppw, total_pairs - pair0);
+        if constexpr (SOFTMAX) {
+            if (lane < nlive) s_stats[lane] = softmax_stats(attn + (pair0 + lane) * P, P);
+            __syncwarp();
         }
+        const bool live = slot < nlive;
+        const int64_t my_pair = pair0 + (live ? slot : 0);
+        const int64_t bq = my_pair / G;
+        const int g = (int)(my_pair - bq * G);
+        const int64_t b = bq / p.Q;
+        const int64_t sample = (b * p.S * G + g) * (int64_t)D;
 
-        auto point = [&](int l, int H, int W, int pt) {
-            const float2 xy = pl[pt];
-            const float a = pa[pt];
-            const Corners c = locate(xy.x, xy.y, H, W);
-            const int64_t level_base = sample_base + (int64_t)lt.start[l] * GD;
-            float dot[4] = {0.f, 0.f, 0.f, 0.f};
-            for (int ch = ch0; ch < D; ch += lph * V) {
-                float2 go[V / 2];
-                if (ch == ch0) {
-#pragma unroll
-                    for (int i = 0; i < V / 2; ++i) go[i] = go0[i];
-                } else {
-                    float f[V];
-                    VT::unpack(ld_stream16(go_row + ch), f);
-#pragma unroll
-                    for (int i = 0; i < V / 2; ++i) go[i] = make_float2(f[2 * i], f[2 * i + 1]);
+        for (int c0 = 0; c0 < P; c0 += PC) {
+            const int pc = min(PC, P - c0);
+            const float inv_pc = 1.f / (float)pc;
+            // ---- pre-pass ----------------------------------------------------------------
+            for (int it = lane; it < ppw * pc; it += 32) {
+                const int sl = (int)(((float)it + 0.5f) * inv_pc);   // it / pc
+                const int j = it - sl * pc;
+                const int pt = c0 + j;
+                uint4 A = make_uint4(0u, 0u, 0u, 0u), Fr = make_uint4(0u, 0u, 0u, 0u);
+                if (sl < nlive) {
+                    const int64_t e = (pair0 + sl) * P + pt;
+                    const float2 xy = ld_stream_f2(loc2 + e);
+                    float a = VT::to_float(attn[e]);
+                    if constexpr (SOFTMAX) {
+                        const float2 st = s_stats[sl];
+                        a = expf(a - st.x) * st.y;
+                        s_prob[sl * P + pt] = a;
+                    }
+                    const int l = (int)(((float)pt + 0.5f) * inv_K);  // pt / K
+                    const PointGeom geo = locate(xy.x, xy.y, lt.H[l], lt.W[l], lt.start[l], GD);
+                    // a skipped point contributes exact zeros whatever its weight holds
+                    const float au = (geo.flags & kInside) ? a : 0.f;
+                    const unsigned flags = geo.flags | (lt.scratch[l] ? kUseScratch : 0u);
+                    A = make_uint4((unsigned)geo.off00, (unsigned)geo.rowstride, flags,
+                                   __float_as_uint(au));
+                    Fr = make_uint4(__float_as_uint(geo.fr), __float_as_uint(geo.fc),
+                                    __float_as_uint(au * geo.Wf), __float_as_uint(au * geo.Hf));
                 }
+                desc[(sl * PC + j) * 2] = A;
+                desc[(sl * PC + j) * 2 + 1] = Fr;
+            }
+            __syncwarp();
+            // ---- gather, scatter, reduce -------------------------------------------------
+            const uint4 *dp = desc + slot * PC * 2;
+            // the trip count is the same for every lane (the shuffles below are warp-wide);
+            // a lane whose channels lie beyond D only contributes zeros
+            for (int cb = 0; cb < D; cb += lph * V) {
+                const int ch = cb + sub * V;
+                const bool first_ch = cb == 0;
+                const bool on_lane = live && ch < D;
+                float2 go[NV2];
+                VT::unpack(on_lane ? ld_stream16(grad_out + my_pair * D + ch)
+                                   : make_uint4(0, 0, 0, 0), go);
+                const T *vc = value + sample + ch;
+                T *gc = grad_value + sample + ch;
+                float *sc = p.scratch + sample + ch;
+#pragma unroll 2
+                for (int j = 0; j < pc; ++j) {
+                    const uint4 A = dp[2 * j];
+                    const uint4 Fr = dp[2 * j + 1];
+                    const unsigned flags = on_lane ? A.z : 0u;
+                    const float a = __uint_as_float(A.w);
+                    const float fr = __uint_as_float(Fr.x), fc = __uint_as_float(Fr.y);
+                    const float wr0 = 1.f - fr, wc0 = 1.f - fc;
+                    const float w[4] = {wr0 * wc0, wr0 * fc, fr * wc0, fr * fc};
+                    const int o00 = (int)A.x, o10 = o00 + (int)A.y;
+                    const int off[4] = {o00, o00 + GD, o10, o10 + GD};
+                    uint4 raw[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (c.ok[j] && live) {
-                        const int64_t idx = level_base + (int64_t)c.off[j] * GD + ch;
-                        float f[V];
-                        VT::unpack(ldg16(value + idx), f);
+                    for (int c = 0; c < 4; ++c) raw[c] = ldg16_if(vc + off[c], flags & (1u << c));
+                    float dot[4];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float2 f[NV2];
+                        VT::unpack(raw[c], f);
                         float2 d2 = make_float2(0.f, 0.f);
-                        const float s = a * c.w[j];
+                        const float s = a * w[c];
                         const float2 s2 = make_float2(s, s);
-                        float gv[V];
+                        float2 gv[NV2];
 #pragma unroll
-                        for (int i = 0; i < V / 2; ++i) {
-                            ffma2(d2, make_float2(f[2 * i], f[2 * i + 1]), go[i]);
-                            const float2 t = fmul2(go[i], s2);
-                            gv[2 * i] = t.x;
-                            gv[2 * i + 1] = t.y;
+                        for (int i = 0; i < NV2; ++i) {
+                            ffma2(d2, f[i], go[i]);
+                            gv[i] = fmul2(go[i], s2);
                         }
-                        dot[j] += d2.x + d2.y;
-                        VT::red_add(grad_value + idx, gv);
+                        dot[c] = d2.x + d2.y;
+                        const bool on = flags & (1u << c);
+                        if constexpr (V == 8) {
+                            if (flags & kUseScratch) {  // uniform over the warp: same point index
+                                if (on) {
+                                    red_add_f32x4(sc + off[c], gv[0], gv[1]);
+                                    red_add_f32x4(sc + off[c] + 4, gv[2], gv[3]);
+                                }
+                            } else {
+                                red_if<T>(gc + off[c], gv, on);
+                            }
+                        } else {
+                            red_if<T>(gc + off[c], gv, on);
+                        }
+                    }
+                    // derivative inside the cell [floor, floor+1); d/da = sample . grad_out
+                    float gx = wr0 * (dot[1] - dot[0]) + fr * (dot[3] - dot[2]);
+                    float gy = wc0 * (dot[2] - dot[0]) + fc * (dot[3] - dot[1]);
+                    float ga = w[0] * dot[0] + w[1] * dot[1] + w[2] * dot[2] + w[3] * dot[3];
+                    for (int o = lph >> 1; o > 0; o >>= 1) {
+                        gx += __shfl_xor_sync(0xffffffffu, gx, o);
+                        gy += __shfl_xor_sync(0xffffffffu, gy, o);
+                        ga += __shfl_xor_sync(0xffffffffu, ga, o);
+                    }
+                    if (sub == 0 && live) {
+                        const int idx = slot * P + c0 + j;
+                        const float2 gl = make_float2(__uint_as_float(Fr.z) * gx,
+                                                      __uint_as_float(Fr.w) * gy);
+                        if (first_ch) {
+                            s_gloc[idx] = gl;
+                            s_gatt[idx] = ga;
+                        } else {
+                            const float2 old = s_gloc[idx];
+                            s_gloc[idx] = make_float2(old.x + gl.x, old.y + gl.y);
+                            s_gatt[idx] += ga;
+                        }
                     }
                 }
             }
-            // d/dx, d/dy inside the cell [floor, floor+1), d/da = sampled value . grad_out
-            float gx = (1.f - c.fr) * (dot[1] - dot[0]) + c.fr * (dot[3] - dot[2]);
-            float gy = (1.f - c.fc) * (dot[2] - dot[0]) + c.fc * (dot[3] - dot[1]);
-            float ga = c.w[0] * dot[0] + c.w[1] * dot[1] + c.w[2] * dot[2] + c.w[3] * dot[3];
-            for (int o = lph >> 1; o > 0; o >>= 1) {
-                gx += __shfl_xor_sync(0xffffffffu, gx, o);
-                gy += __shfl_xor_sync(0xffffffffu, gy, o);
-                ga += __shfl_xor_sync(0xffffffffu, ga, o);
-            }
-            if (sub == 0 && live) {
-                // skipped points get exact zeros, whatever their weight holds
-                pl[pt] = c.inside ? make_float2((float)W * a * gx, (float)H * a * gy)
-                                  : make_float2(0.f, 0.f);
-                pg[pt] = c.inside ? ga : 0.f;
-            }
-        };
-
-        for (int l = 0; l < L; ++l) {
-            const int H = lt.H[l], W = lt.W[l];
-            if constexpr (KT > 0) {
-#pragma unroll
-                for (int k = 0; k < KT; ++k) point(l, H, W, l * KT + k);
-            } else {
-                for (int k = 0; k < K; ++k) point(l, H, W, l * K + k);
-            }
+            __syncwarp();
         }
+
+        // ---- softmax Jacobian and contiguous write-out of the group's gradients -------------
+        if constexpr (SOFTMAX) {
+            if (lane < nlive) {
+                float inner = 0.f;
+                for (int i = 0; i < P; ++i) inner += s_prob[lane * P + i] * s_gatt[lane * P + i];
+                s_stats[lane].x = inner;
+            }
+            __syncwarp();
+        }
+        float2 *gl_out = reinterpret_cast<float2 *>(p.grad_loc) + pair0 * P;
+        T *ga_out = reinterpret_cast<T *>(p.grad_attn) + pair0 * P;
+        for (int idx = lane; idx < nlive * P; idx += 32) {
+            float ga = s_gatt[idx];
+            if constexpr (SOFTMAX) {
+                const int sl = (int)(((float)idx + 0.5f) * inv_P);
+                ga = s_prob[idx] * (ga - s_stats[sl].x);
+            }
+            st_stream_f2(gl_out + idx, s_gloc[idx]);
+            ga_out[idx] = VT::from_float(ga);
+        }
+        __syncwarp();
     }
+}
+
+// ---- grad_value preparation and finalisation for the float32-scratch levels ------------------
+__device__ __forceinline__ int level_of(const LevelTable &lt, int L, int s) {
+    int l = 0;
+    for (int i = 1; i < L; ++i)
+        if (s >= lt.start[i]) l = i;
+    return l;
+}
+
+// Clears, per 16-byte vector of grad_value, either the vector itself (direct levels) or the
+// matching float32 scratch elements (scratch levels, whose grad_value is written by finalize).
+template <typename T>
+__global__ void __launch_bounds__(256) prepare_kernel(const Params p) {
+    __shared__ LevelTable lt;
+    load_level_table(lt, p);
     __syncthreads();
-
-    if constexpr (SOFTMAX) {
-        for (int pair = threadIdx.x; pair < npairs; pair += kThreads) {
-            const float *pr = sAttn + pair * P;
-            float *g = sGrad + pair * P;
-            float inner = 0.f;
-            for (int i = 0; i < P; ++i) inner += pr[i] * g[i];
-            for (int i = 0; i < P; ++i) g[i] = pr[i] * (g[i] - inner);
-        }
-        __syncthreads();
-    }
-
-    // coalesced write-out of the tile's grad_loc (float32) and grad_attn (T)
-    {
-        const int n = npairs * P * 2;
-        float *dst = p.grad_loc + bq0 * G * P * 2;
-        const int n4 = n >> 2;
-        for (int i = threadIdx.x; i < n4; i += kThreads)
-            st_stream16(reinterpret_cast<uint4 *>(dst) + i, reinterpret_cast<const uint4 *>(sLoc)[i]);
-        for (int i = (n4 << 2) + threadIdx.x; i < n; i += kThreads) dst[i] = sLoc[i];
-    }
-    {
-        const int n = npairs * P;
-        T *dst = reinterpret_cast<T *>(p.grad_attn) + bq0 * G * P;
-        const int nv = n / V;
-        for (int i = threadIdx.x; i < nv; i += kThreads) {
-            float f[V];
+    constexpr int V = VecTraits<T>::kVec;
+    const int vec_per_row = p.G * p.D / V;
+    const int64_t total = p.B * p.S * vec_per_row;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < total;
+         v += (int64_t)gridDim.x * blockDim.x) {
+        const int s = (int)((v / vec_per_row) % p.S);
+        if (lt.scratch[level_of(lt, p.L, s)]) {
+            uint4 *dst = reinterpret_cast<uint4 *>(p.scratch + v * V);
 #pragma unroll
-            for (int j = 0; j < V; ++j) f[j] = sGrad[i * V + j];
-            st_stream16(reinterpret_cast<uint4 *>(dst) + i, VT::pack(f));
+            for (int i = 0; i < V / 4; ++i) dst[i] = zero;
+        } else {
+            reinterpret_cast<uint4 *>(p.grad_value)[v] = zero;
         }
-        for (int i = nv * V + threadIdx.x; i < n; i += kThreads) dst[i] = VT::from_float(sGrad[i]);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) finalize_kernel(const Params p) {
+    __shared__ LevelTable lt;
+    load_level_table(lt, p);
+    __syncthreads();
+    using VT = VecTraits<T>;
+    constexpr int V = VT::kVec;
+    const int vec_per_row = p.G * p.D / V;
+    const int64_t total = p.B * p.S * vec_per_row;
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < total;
+         v += (int64_t)gridDim.x * blockDim.x) {
+        const int s = (int)((v / vec_per_row) % p.S);
+        if (!lt.scratch[level_of(lt, p.L, s)]) continue;
+        const float4 *src = reinterpret_cast<const float4 *>(p.scratch + v * V);
+        float2 f[V / 2];
+#pragma unroll
+        for (int i = 0; i < V / 4; ++i) {
+            const float4 t = src[i];
+            f[2 * i] = make_float2(t.x, t.y);
+            f[2 * i + 1] = make_float2(t.z, t.w);
+        }
+        reinterpret_cast<uint4 *>(p.grad_value)[v] = VT::pack(f);
     }
 }
 
 template <typename T, bool SOFTMAX>
 cudaError_t launch_typed(const Params &p, cudaStream_t stream) {
     const size_t smem = backward_smem_bytes(p, SOFTMAX);
-    auto go = [&](auto kernel) -> cudaError_t {
-        if (smem > 48 * 1024) {  // opt in to large dynamic shared memory only when needed
-            cudaError_t e = cudaFuncSetAttribute(
-                kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return e;
-        }
-        kernel<<<(unsigned)p.num_tiles, kThreads, smem, stream>>>(p);
-        return cudaGetLastError();
-    };
-    switch (p.K) {
-        case 4: return go(backward_kernel<T, 4, SOFTMAX>);
-        case 8: return go(backward_kernel<T, 8, SOFTMAX>);
-        default: return go(backward_kernel<T, 0, SOFTMAX>);
+    auto kernel = backward_kernel<T, SOFTMAX>;
+    if (smem > 48 * 1024) {  // opt in to large dynamic shared memory only when needed
+        cudaError_t e =
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
     }
+    kernel<<<p.grid, p.threads, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+unsigned sweep_grid(const Params &p, int vec) {
+    const int64_t total = p.B * p.S * (p.G * p.D / vec);
+    const int64_t blocks = (total + 256 * 4 - 1) / (256 * 4);   // ~4 vectors per thread
+    return (unsigned)(blocks < 1 ? 1 : (blocks > 148 * 16 ? 148 * 16 : blocks));
 }
 
 }  // namespace
 
 size_t backward_smem_bytes(const Params &p, bool softmax) {
-    return (size_t)p.tile_queries * p.G * p.L * p.K * (softmax ? 4 : 3) * sizeof(float);
+    const size_t nwarps = p.threads / 32;
+    const size_t stage_floats = backward_stage_floats(32 >> p.lph_log2, p.L * p.K, softmax);
+    return nwarps * (kDescPerWarp * 32 + stage_floats * sizeof(float));
 }
 
 cudaError_t launch_backward(const Params &p, int dtype, bool softmax, cudaStream_t stream) {
@@ -240,6 +352,26 @@ cudaError_t launch_backward(const Params &p, int dtype, bool softmax, cudaStream
                            : launch_typed<__nv_bfloat16, false>(p, stream);
         default: return cudaErrorInvalidValue;
     }
+}
+
+cudaError_t launch_prepare_grad_value(const Params &p, int dtype, cudaStream_t stream) {
+    if (dtype == 1)
+        prepare_kernel<__half><<<sweep_grid(p, 8), 256, 0, stream>>>(p);
+    else if (dtype == 2)
+        prepare_kernel<__nv_bfloat16><<<sweep_grid(p, 8), 256, 0, stream>>>(p);
+    else
+        return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_finalize_grad_value(const Params &p, int dtype, cudaStream_t stream) {
+    if (dtype == 1)
+        finalize_kernel<__half><<<sweep_grid(p, 8), 256, 0, stream>>>(p);
+    else if (dtype == 2)
+        finalize_kernel<__nv_bfloat16><<<sweep_grid(p, 8), 256, 0, stream>>>(p);
+    else
+        return cudaErrorInvalidValue;
+    return cudaGetLastError();
 }
 
 }  // namespace msda_b200

@@ -3,140 +3,158 @@
 // Replaces the reference's forward path
 //   sources/deformops/backends/cuda/include/msda_forward.cuh:13-123 (kernel)
 //   sources/deformops/backends/cuda/include/interpolate.cuh:14-72   (bilinear gather)
-// with a design of its own: one CTA stages the sampling locations and weights of a tile
-// of queries in shared memory with coalesced 16-byte streaming loads (each is read from
-// HBM exactly once), then every slot of LPH lanes walks the points of one (query, head)
-// pair and gathers the four bilinear corners with one 16-byte load per lane along the
-// head dimension, accumulating in float32 with packed f32x2 FMAs.
+// with a design of its own.  A warp owns a group of 32/LPH (query, head) pairs - for
+// bf16 heads of 32 channels, the 8 heads of one query.  Per group:
+//   1. pre-pass: the lanes read the group's sampling locations and weights straight from
+//      global memory (contiguous, streaming, each byte exactly once), and ONE lane per
+//      point turns them into a 32-byte descriptor in shared memory: corner offset, row
+//      stride, validity flags, and the four corner weights already multiplied by the
+//      attention weight (softmax-normalised on the fly when asked);
+//   2. gather: each slot's lanes read their point's descriptor as two broadcast 16-byte
+//      shared loads, issue the four corner loads (16 bytes per lane along the head
+//      dimension, predicated off for corners outside the level - nothing is clamped) and
+//      accumulate in float32 with packed f32x2 FMAs;
+//   3. one 16-byte streaming store per lane: a warp writes a query's G*D row contiguously.
 #include "msda_common.cuh"
 
 namespace msda_b200 {
 
 namespace {
 
-template <typename T, int KT, bool SOFTMAX>
-__global__ void __launch_bounds__(kThreads, 4) forward_kernel(const Params p) {
+template <typename T, bool SOFTMAX>
+__global__ void __launch_bounds__(256, 4) forward_kernel(const Params p) {
     using VT = VecTraits<T>;
     constexpr int V = VT::kVec;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int NV2 = V / 2;
+    extern __shared__ uint4 smem[];
     __shared__ LevelTable lt;
 
-    const int G = p.G, D = p.D, L = p.L;
-    const int K = KT > 0 ? KT : p.K;
-    const int P = L * K;
-    const int TQ = p.tile_queries;
-    float *sLoc = reinterpret_cast<float *>(smem_raw);   // [pair][P][2]
-    float *sAttn = sLoc + (size_t)TQ * G * P * 2;         // [pair][P]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nwarps = blockDim.x >> 5;
+    const int lph = 1 << p.lph_log2;
+    const int ppw = 32 >> p.lph_log2;          // pairs per warp (group size)
+    const int PC = p.point_chunk;
+    const int G = p.G, D = p.D, K = p.K;
+    const int P = p.L * K;
+    const int GD = G * D;
+    const float inv_K = 1.f / (float)K;
+
+    uint4 *desc = smem + (size_t)warp * (kDescPerWarp * 2);                 // [slot][PC][2]
+    float2 *stats = reinterpret_cast<float2 *>(smem + (size_t)nwarps * (kDescPerWarp * 2)) +
+                    warp * 32;                                              // softmax only
 
     load_level_table(lt, p);
-
-    const int64_t total_q = p.B * p.Q;
-    const int64_t bq0 = (int64_t)blockIdx.x * TQ;
-    const int nq = (int)min((int64_t)TQ, total_q - bq0);
-    const int npairs = nq * G;
-
-    stage_f32(sLoc, p.loc + bq0 * G * P * 2, npairs * P * 2);
-    stage_as_f32<T>(sAttn, reinterpret_cast<const T *>(p.attn) + bq0 * G * P, npairs * P);
     __syncthreads();
 
-    if constexpr (SOFTMAX) {
-        // normalise each pair's L*K logits in place; skipped points stay in the denominator
-        for (int pair = threadIdx.x; pair < npairs; pair += kThreads) {
-            float *a = sAttn + pair * P;
-            float m = -INFINITY;
-            for (int i = 0; i < P; ++i) m = fmaxf(m, a[i]);
-            float sum = 0.f;
-            for (int i = 0; i < P; ++i) {
-                const float e = expf(a[i] - m);
-                a[i] = e;
-                sum += e;
-            }
-            const float inv = 1.f / sum;
-            for (int i = 0; i < P; ++i) a[i] *= inv;
-        }
-        __syncthreads();
-    }
-
-    const int lph = 1 << p.lph_log2;
-    const int slot = threadIdx.x >> p.lph_log2;
-    const int sub = threadIdx.x & (lph - 1);
-    const int nslots = kThreads >> p.lph_log2;
-    const int GD = G * D;
+    const int64_t total_pairs = p.B * p.Q * G;
+    const int slot = lane >> p.lph_log2;
+    const int sub = lane & (lph - 1);
     const T *value = reinterpret_cast<const T *>(p.value);
+    const T *attn = reinterpret_cast<const T *>(p.attn);
+    const float2 *loc2 = reinterpret_cast<const float2 *>(p.loc);
     T *out = reinterpret_cast<T *>(p.out);
 
-    for (int pair = slot; pair < npairs; pair += nslots) {
-        const int64_t bq = bq0 + pair / G;
-        const int g = pair % G;
+    for (int64_t group = (int64_t)blockIdx.x * nwarps + warp; group < p.num_groups;
+         group += (int64_t)gridDim.x * nwarps) {
+        const int64_t pair0 = group * ppw;
+        const int nlive = (int)min((int64_t)ppw, total_pairs - pair0);
+        if constexpr (SOFTMAX) {
+            if (lane < nlive) stats[lane] = softmax_stats(attn + (pair0 + lane) * P, P);
+            __syncwarp();
+        }
+        const bool live = slot < nlive;
+        const int64_t my_pair = pair0 + (live ? slot : 0);
+        const int64_t bq = my_pair / G;
+        const int g = (int)(my_pair - bq * G);
         const int64_t b = bq / p.Q;
-        const float2 *pl = reinterpret_cast<const float2 *>(sLoc) + pair * P;
-        const float *pa = sAttn + pair * P;
-        for (int ch = sub * V; ch < D; ch += lph * V) {
-            float2 acc[V / 2];
+        const T *vb = value + (b * p.S * G + g) * (int64_t)D;
+
+        float2 acc[NV2];
+        for (int c0 = 0; c0 < P; c0 += PC) {
+            const int pc = min(PC, P - c0);
+            const float inv_pc = 1.f / (float)pc;
+            // ---- pre-pass: one lane per (pair, point) builds the descriptor --------------
+            for (int it = lane; it < ppw * pc; it += 32) {
+                const int sl = (int)(((float)it + 0.5f) * inv_pc);   // it / pc
+                const int j = it - sl * pc;
+                const int pt = c0 + j;
+                uint4 A = make_uint4(0u, 0u, 0u, 0u), Wt = make_uint4(0u, 0u, 0u, 0u);
+                if (sl < nlive) {
+                    const int64_t e = (pair0 + sl) * P + pt;
+                    const float2 xy = ld_stream_f2(loc2 + e);
+                    float a = VT::to_float(attn[e]);
+                    if constexpr (SOFTMAX) {
+                        const float2 st = stats[sl];
+                        a = expf(a - st.x) * st.y;
+                    }
+                    const int l = (int)(((float)pt + 0.5f) * inv_K);  // pt / K
+                    const PointGeom geo = locate(xy.x, xy.y, lt.H[l], lt.W[l], lt.start[l], GD);
+                    const float wr0 = 1.f - geo.fr, wc0 = 1.f - geo.fc;
+                    A = make_uint4((unsigned)geo.off00, (unsigned)geo.rowstride, geo.flags, 0u);
+                    Wt = make_uint4(__float_as_uint(a * (wr0 * wc0)),
+                                    __float_as_uint(a * (wr0 * geo.fc)),
+                                    __float_as_uint(a * (geo.fr * wc0)),
+                                    __float_as_uint(a * (geo.fr * geo.fc)));
+                }
+                desc[(sl * PC + j) * 2] = A;
+                desc[(sl * PC + j) * 2 + 1] = Wt;
+            }
+            __syncwarp();
+            // ---- gather ------------------------------------------------------------------
+            const uint4 *dp = desc + slot * PC * 2;
+            for (int ch = sub * V; ch < D; ch += lph * V) {
+                if (c0 == 0) {
 #pragma unroll
-            for (int i = 0; i < V / 2; ++i) acc[i] = make_float2(0.f, 0.f);
-            const T *vb = value + (b * p.S * G + g) * (int64_t)D + ch;
-            auto sample_point = [&](const T *vl, int H, int W, int pt) {
-                const float2 xy = pl[pt];
-                const float a = pa[pt];
-                const Corners c = locate(xy.x, xy.y, H, W);
+                    for (int i = 0; i < NV2; ++i) acc[i] = make_float2(0.f, 0.f);
+                }
+                const T *vc = vb + ch;
+#pragma unroll 2
+                for (int j = 0; j < pc; ++j) {
+                    const uint4 A = dp[2 * j];
+                    const uint4 Wt = dp[2 * j + 1];
+                    const unsigned flags = live ? A.z : 0u;
+                    const int o00 = (int)A.x, o10 = o00 + (int)A.y;
+                    const uint4 r0 = ldg16_if(vc + o00, flags & kCorner00);
+                    const uint4 r1 = ldg16_if(vc + (o00 + GD), flags & kCorner01);
+                    const uint4 r2 = ldg16_if(vc + o10, flags & kCorner10);
+                    const uint4 r3 = ldg16_if(vc + (o10 + GD), flags & kCorner11);
+                    const uint4 raw[4] = {r0, r1, r2, r3};
+                    const float w[4] = {__uint_as_float(Wt.x), __uint_as_float(Wt.y),
+                                        __uint_as_float(Wt.z), __uint_as_float(Wt.w)};
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (c.ok[j]) {
-                        float f[V];
-                        VT::unpack(ldg16(vl + (int64_t)c.off[j] * GD), f);
-                        const float wa = a * c.w[j];
-                        const float2 wa2 = make_float2(wa, wa);
+                    for (int c = 0; c < 4; ++c) {
+                        float2 f[NV2];
+                        VT::unpack(raw[c], f);
+                        const float2 w2 = make_float2(w[c], w[c]);
 #pragma unroll
-                        for (int i = 0; i < V / 2; ++i)
-                            ffma2(acc[i], make_float2(f[2 * i], f[2 * i + 1]), wa2);
+                        for (int i = 0; i < NV2; ++i) ffma2(acc[i], f[i], w2);
                     }
                 }
-            };
-            for (int l = 0; l < L; ++l) {
-                const int H = lt.H[l], W = lt.W[l];
-                const T *vl = vb + (int64_t)lt.start[l] * GD;
-                if constexpr (KT > 0) {
-#pragma unroll
-                    for (int k = 0; k < KT; ++k) sample_point(vl, H, W, l * KT + k);
-                } else {
-                    for (int k = 0; k < K; ++k) sample_point(vl, H, W, l * K + k);
-                }
+                if (c0 + PC >= P && live) st_stream16(out + my_pair * D + ch, VT::pack(acc));
             }
-            float r[V];
-#pragma unroll
-            for (int i = 0; i < V / 2; ++i) {
-                r[2 * i] = acc[i].x;
-                r[2 * i + 1] = acc[i].y;
-            }
-            st_stream16(out + (bq * G + g) * (int64_t)D + ch, VT::pack(r));
+            __syncwarp();
         }
     }
 }
 
 template <typename T, bool SOFTMAX>
 cudaError_t launch_typed(const Params &p, cudaStream_t stream) {
-    const size_t smem = forward_smem_bytes(p);
-    auto go = [&](auto kernel) -> cudaError_t {
-        if (smem > 48 * 1024) {  // opt in to large dynamic shared memory only when needed
-            cudaError_t e = cudaFuncSetAttribute(
-                kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return e;
-        }
-        kernel<<<(unsigned)p.num_tiles, kThreads, smem, stream>>>(p);
-        return cudaGetLastError();
-    };
-    switch (p.K) {
-        case 4: return go(forward_kernel<T, 4, SOFTMAX>);
-        case 8: return go(forward_kernel<T, 8, SOFTMAX>);
-        default: return go(forward_kernel<T, 0, SOFTMAX>);
+    const size_t smem = forward_smem_bytes(p, SOFTMAX);
+    auto kernel = forward_kernel<T, SOFTMAX>;
+    if (smem > 48 * 1024) {  // opt in to large dynamic shared memory only when needed
+        cudaError_t e =
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
     }
+    kernel<<<p.grid, p.threads, smem, stream>>>(p);
+    return cudaGetLastError();
 }
 
 }  // namespace
 
-size_t forward_smem_bytes(const Params &p) {
-    return (size_t)p.tile_queries * p.G * p.L * p.K * 3 * sizeof(float);
+size_t forward_smem_bytes(const Params &p, bool softmax) {
+    const size_t nwarps = p.threads / 32;
+    return nwarps * kDescPerWarp * 32 + (softmax ? nwarps * 32 * sizeof(float2) : 0);
 }
 
 cudaError_t launch_forward(const Params &p, int dtype, bool softmax, cudaStream_t stream) {

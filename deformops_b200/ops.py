@@ -152,14 +152,20 @@ def _make_backward(softmax: bool) -> Callable[..., tuple[Tensor, Tensor, Tensor]
         shim = load_library()
         value, loc, attn, grad_output = map(_aligned, (value, loc, attn, grad_output))
         stream = torch.cuda.current_stream(value.device).cuda_stream
+        # float32 accumulator for the coarse levels of a 16-bit grad_value; comes from torch's
+        # caching allocator, only the rows of the levels that use it are ever touched
+        nbytes = shim.scratch_bytes(B, S, G, D, DTYPE_CODES[value.dtype]) if Q > 0 else 0
+        scratch = (torch.empty(nbytes // 4, dtype=torch.float32, device=value.device)
+                   if nbytes else None)
         st = shim.backward(_ptr(value), _ptr(spatial_shapes), _ptr(level_start_index), _ptr(loc),
                            _ptr(attn), _ptr(grad_output), _ptr(grad_value), _ptr(grad_loc),
-                           _ptr(grad_attn), B, S, G, D, Q, L, K, DTYPE_CODES[value.dtype],
+                           _ptr(grad_attn), _ptr(scratch) if nbytes else None, nbytes, 0,
+                           B, S, G, D, Q, L, K, DTYPE_CODES[value.dtype],
                            int(softmax), 1, value.device.index, ctypes.c_void_p(stream))
         if st != 0:
             _raise(shim, st, "msda_b200_backward")
-        launch_counter.kernels += 1 if Q > 0 else 0
-        launch_counter.memsets += 1
+        launch_counter.kernels += (3 if nbytes else 1) if Q > 0 else 0
+        launch_counter.memsets += 0 if nbytes else 1
         return grad_value, grad_loc, grad_attn
 
     return backward_cuda

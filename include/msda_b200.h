@@ -24,9 +24,8 @@
  *   - Thread safety: no mutable global state; concurrent calls from several host
  *     threads (for example the autograd thread) are allowed.
  *   - Supported: dtype f32 / f16 / bf16; D a multiple of 4 (f32) or 8 (f16, bf16);
- *     1 <= L <= 16; any K >= 1 (K = 4 and K = 8 have unrolled instantiations);
- *     S < 2^31.  B == 0 or Q == 0 is a successful no-op (backward still clears
- *     grad_value).
+ *     1 <= L <= 16; any K >= 1; S*G*D < 2^31 per sample.  B == 0 or Q == 0 is a
+ *     successful no-op (backward still clears grad_value).
  */
 #ifndef MSDA_B200_H_
 #define MSDA_B200_H_
@@ -37,7 +36,7 @@
 extern "C" {
 #endif
 
-#define MSDA_B200_ABI_VERSION 1
+#define MSDA_B200_ABI_VERSION 2
 
 enum msda_b200_dtype { MSDA_B200_F32 = 0, MSDA_B200_F16 = 1, MSDA_B200_BF16 = 2 };
 
@@ -75,31 +74,48 @@ int msda_b200_forward(const void *value, const int64_t *spatial_shapes,
  * grad_loc (float32) and grad_attn (`dtype`; gradient w.r.t. the raw logits when
  * apply_softmax != 0).  grad_loc and grad_attn are written in full (skipped points get
  * exact zeros).  If zero_grad_value != 0 the call first clears grad_value on `stream`;
- * pass 0 to accumulate into a buffer the caller prepared.
+ * pass 0 to accumulate into a buffer the caller prepared (scratch must then be NULL).
+ *
+ * scratch / scratch_adds (16-bit dtypes only): summing hundreds of contributions per
+ * element in f16/bf16 loses accuracy on coarse pyramid levels.  When `scratch` is not
+ * NULL it must hold msda_b200_backward_scratch_bytes(...) bytes (a float32 image of
+ * grad_value; only the rows of the levels that use it are touched).  A level then
+ * accumulates in float32 when its expected additions per element, 4*K*Q / (H*W), exceed
+ * `scratch_adds`; pass 0 for the library default (32 for bf16, 512 for f16).  Such levels
+ * are converted to `dtype` at the end of the call.  With scratch == NULL every level uses
+ * direct 16-bit reductions (fastest, least accurate).  Ignored for float32.
  *
  * Replaces: boxed op `<prefix>_backward` / `<prefix>_softmax_backward`
  *   sources/deformops/backends/cuda/include/msda_boxed.cuh:32-53
  *   sources/deformops/backends/cuda/include/msda_launch.cuh:141-275 (backward_cuda)
  *   schema sources/deformops/backends/cuda/_schema.py:24-29
- * Differences: gradients are caller-allocated; grad_value and grad_attn are produced
- * directly in `dtype` (no float32 scratch copy and cast-back pass).
+ * Differences: gradients and scratch are caller-allocated; grad_attn is produced directly
+ * in `dtype`; the float32 accumulator covers only the levels that need it instead of the
+ * whole tensor (msda_launch.cuh:188-197, 263-273 upcast, clear and cast back everything).
  */
 int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
                        const int64_t *level_start_index, const float *loc, const void *attn,
                        const void *grad_out, void *grad_value, float *grad_loc, void *grad_attn,
-                       int64_t B, int64_t S, int64_t G, int64_t D, int64_t Q, int64_t L,
-                       int64_t K, int dtype, int apply_softmax, int zero_grad_value, int device,
-                       void *stream);
+                       void *scratch, int64_t scratch_bytes, int64_t scratch_adds, int64_t B,
+                       int64_t S, int64_t G, int64_t D, int64_t Q, int64_t L, int64_t K, int dtype,
+                       int apply_softmax, int zero_grad_value, int device, void *stream);
+
+/*
+ * Bytes of float32 scratch msda_b200_backward can use for a shape: B*S*G*D*4 for the
+ * 16-bit dtypes, 0 for float32.
+ * Replaces: the `new_zeros` float32 grad_value of msda_launch.cuh:188-197.
+ */
+int64_t msda_b200_backward_scratch_bytes(int64_t B, int64_t S, int64_t G, int64_t D, int dtype);
 
 /*
  * Launch geometry the library would use for a shape, for harnesses that count launches
- * or size grids: number of CTAs, queries per CTA tile and dynamic shared memory of the
- * forward (*_fwd) and backward (*_bwd) kernels.  Pure function of its arguments.
+ * or size grids: number of CTAs, threads per CTA and dynamic shared memory of the forward
+ * (*_fwd) and backward (*_bwd) kernels.  Pure function of its arguments.
  * Replaces: forward_thread_layout / backward_thread_layout
  *   sources/deformops/core/tuning.py:55-133, include/msda_launch.cuh:26-52
  */
 int msda_b200_launch_geometry(int64_t B, int64_t G, int64_t D, int64_t Q, int64_t L, int64_t K,
-                              int dtype, int apply_softmax, int64_t *grid, int *tile_queries,
+                              int dtype, int apply_softmax, int64_t *grid, int *threads,
                               int64_t *smem_fwd, int64_t *smem_bwd);
 
 #ifdef __cplusplus

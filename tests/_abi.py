@@ -40,18 +40,23 @@ def abi_forward(value, shapes, starts, loc, attn, *, softmax=False, stream=None)
     return out
 
 
-def abi_backward(value, shapes, starts, loc, attn, grad_out, *, softmax=False, zero=True):
+def abi_backward(value, shapes, starts, loc, attn, grad_out, *, softmax=False, zero=True,
+                 scratch=True, scratch_adds=0):
+    """``scratch=True`` hands the call the float32 accumulator the product path uses for
+    16-bit dtypes; ``scratch=False`` forces direct 16-bit reductions on every level."""
     shim = load_library()
     B, S, G, D, Q, L, K = dims(value, loc)
     # poison the outputs: the call must overwrite every element
     grad_value = torch.full_like(value, float("nan")) if zero else torch.zeros_like(value)
     grad_loc = torch.full_like(loc, float("nan"))
     grad_attn = torch.full_like(attn, float("nan"))
+    nbytes = shim.scratch_bytes(B, S, G, D, DTYPE_CODES[value.dtype]) if (scratch and zero) else 0
+    buf = torch.full((max(nbytes // 4, 1),), float("nan"), device=value.device) if nbytes else None
     s = torch.cuda.current_stream().cuda_stream
     st = shim.backward(_p(value), _p(shapes), _p(starts), _p(loc), _p(attn), _p(grad_out),
-                       _p(grad_value), _p(grad_loc), _p(grad_attn), B, S, G, D, Q, L, K,
-                       DTYPE_CODES[value.dtype], int(softmax), int(zero), value.device.index,
-                       ctypes.c_void_p(s))
+                       _p(grad_value), _p(grad_loc), _p(grad_attn), _p(buf), nbytes, scratch_adds,
+                       B, S, G, D, Q, L, K, DTYPE_CODES[value.dtype], int(softmax), int(zero),
+                       value.device.index, ctypes.c_void_p(s))
     assert st == 0, shim.last_error()
     return grad_value, grad_loc, grad_attn
 

@@ -48,7 +48,9 @@ def test_non_contiguous_split_weights_int32_tables_and_16bit_locations():
     c, t = _case("small_b")
     B, Q, G, L, K, _ = c["loc"].shape
     value = t["value"].transpose(1, 2).contiguous().transpose(1, 2)      # strided view
-    loc = t["loc"].flip(-1).contiguous().flip(-1)
+    padded = torch.zeros(*t["loc"].shape[:-1], 3, device="cuda")
+    padded[..., :2] = t["loc"]
+    loc = padded[..., :2]                                                # strided view
     attn5 = t["attn_linear"].view(B, Q, G, L, K)
     v, l, a = (x.detach().requires_grad_(True) for x in (value, loc, attn5))
     assert not v.is_contiguous() and not l.is_contiguous()
@@ -131,7 +133,8 @@ def test_fake_tensor_backward_and_compile():
 
 
 def test_errors_before_launch():
-    from deformops_b200.registry import Backend, NoBackendError, msda  # type: ignore[attr-defined]
+    from deformops_b200 import NoBackendError
+    from deformops_b200.registry import Backend, msda
 
     _, t = _case("small_b")
     args = [t["value"], t["shapes"], t["starts"], t["loc"], t["attn_linear"]]
