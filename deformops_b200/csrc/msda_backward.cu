@@ -72,6 +72,7 @@ __global__ void __launch_bounds__(256, 3) backward_kernel(const Params p) {
     const int lph = 1 << p.lph_log2;
     const int ppw = 32 >> p.lph_log2;
     const int PC = p.point_chunk;
+    const int DS = 2 * PC + 1;                 // uint4 stride between slots (odd: no bank conflicts)
     const int G = p.G, D = p.D, K = p.K;
     const int P = p.L * K;
     const int GD = G * D;
@@ -79,9 +80,9 @@ __global__ void __launch_bounds__(256, 3) backward_kernel(const Params p) {
     const float inv_P = 1.f / (float)P;
 
     // per-warp shared memory: descriptors, then staged gradients of the whole group
-    uint4 *desc = smem + (size_t)warp * (kDescPerWarp * 2);
+    uint4 *desc = smem + (size_t)warp * kDescWarpVec;
     const int stage_floats = backward_stage_floats(ppw, P, SOFTMAX);
-    float *stage = reinterpret_cast<float *>(smem + (size_t)nwarps * (kDescPerWarp * 2)) +
+    float *stage = reinterpret_cast<float *>(smem + (size_t)nwarps * kDescWarpVec) +
                    (size_t)warp * stage_floats;
     float2 *s_stats = reinterpret_cast<float2 *>(stage);         // [32] softmax (max, 1/sum)
     float2 *s_gloc = s_stats + 32;                               // [ppw*P] (dx, dy)
@@ -143,12 +144,12 @@ __global__ void __launch_bounds__(256, 3) backward_kernel(const Params p) {
                     Fr = make_uint4(__float_as_uint(geo.fr), __float_as_uint(geo.fc),
                                     __float_as_uint(au * geo.Wf), __float_as_uint(au * geo.Hf));
                 }
-                desc[(sl * PC + j) * 2] = A;
-                desc[(sl * PC + j) * 2 + 1] = Fr;
+                desc[sl * DS + 2 * j] = A;
+                desc[sl * DS + 2 * j + 1] = Fr;
             }
             __syncwarp();
             // ---- gather, scatter, reduce -------------------------------------------------
-            const uint4 *dp = desc + slot * PC * 2;
+            const uint4 *dp = desc + slot * DS;
             // the trip count is the same for every lane (the shuffles below are warp-wide);
             // a lane whose channels lie beyond D only contributes zeros
             for (int cb = 0; cb < D; cb += lph * V) {
@@ -336,7 +337,7 @@ unsigned sweep_grid(const Params &p, int vec) {
 size_t backward_smem_bytes(const Params &p, bool softmax) {
     const size_t nwarps = p.threads / 32;
     const size_t stage_floats = backward_stage_floats(32 >> p.lph_log2, p.L * p.K, softmax);
-    return nwarps * (kDescPerWarp * 32 + stage_floats * sizeof(float));
+    return nwarps * (kDescWarpVec * 16 + stage_floats * sizeof(float));
 }
 
 cudaError_t launch_backward(const Params &p, int dtype, bool softmax, cudaStream_t stream) {

@@ -29,6 +29,9 @@ namespace msda_b200 {
 
 constexpr int kMaxLevels = 16;           // level table kept in shared memory
 constexpr int kDescPerWarp = 128;        // descriptors (32 B each) a warp holds at a time
+// uint4 words of descriptor storage per warp: every slot's row is padded by one uint4 so that
+// the 8 (or fewer) slots of a warp read their 16-byte descriptor halves from distinct banks
+constexpr int kDescWarpVec = 2 * kDescPerWarp + 32;
 
 struct Params {
     const void *value;
@@ -154,6 +157,11 @@ __device__ __forceinline__ float2 fmul2(const float2 a, const float2 b) {
     return r;
 }
 
+// read-only 16-byte gather load
+__device__ __forceinline__ uint4 ldg16(const void *p) {
+    return __ldg(reinterpret_cast<const uint4 *>(p));
+}
+
 // Read-only 16-byte gather load, predicated: returns zeros and touches no memory when
 // `pred` is false.  Not volatile, so the compiler may batch the loads of several points.
 __device__ __forceinline__ uint4 ldg16_if(const void *p, bool pred) {
@@ -226,6 +234,7 @@ struct PointGeom {
     int off00;       // element offset of corner (r0, c0) from the sample's first element
     int rowstride;   // elements between image rows of this level: W * G * D
     unsigned flags;
+    int r0, c0;      // integer pixel of corner (r0, c0); -1 is possible on either axis
     float fr, fc;    // fractional parts along height / width
     float Hf, Wf;
 };
@@ -251,6 +260,8 @@ __device__ __forceinline__ PointGeom locate(float x, float y, int H, int W, int 
     g.flags = (r_ok0 && c_ok0 ? kCorner00 : 0u) | (r_ok0 && c_ok1 ? kCorner01 : 0u) |
               (r_ok1 && c_ok0 ? kCorner10 : 0u) | (r_ok1 && c_ok1 ? kCorner11 : 0u) |
               (inside ? kInside : 0u);
+    g.r0 = r0;
+    g.c0 = c0;
     g.off00 = (start + r0 * W + c0) * GD;
     g.rowstride = W * GD;
     return g;

@@ -7,25 +7,36 @@
 // bf16 heads of 32 channels, the 8 heads of one query.  Per group:
 //   1. pre-pass: the lanes read the group's sampling locations and weights straight from
 //      global memory (contiguous, streaming, each byte exactly once), and ONE lane per
-//      point turns them into a 32-byte descriptor in shared memory: corner offset, row
-//      stride, validity flags, and the four corner weights already multiplied by the
+//      point turns them into a 32-byte descriptor in shared memory: the four corner
+//      offsets and the four corner weights already multiplied by the
 //      attention weight (softmax-normalised on the fly when asked);
 //   2. gather: each slot's lanes read their point's descriptor as two broadcast 16-byte
 //      shared loads, issue the four corner loads (16 bytes per lane along the head
-//      dimension, predicated off for corners outside the level - nothing is clamped) and
-//      accumulate in float32 with packed f32x2 FMAs;
+//      dimension; a corner outside the level has weight zero and its load is redirected to
+//      the nearest pixel inside, so no value is ever blended in from a clamped position)
+//      and accumulate in float32 with packed f32x2 FMAs;
 //   3. one 16-byte streaming store per lane: a warp writes a query's G*D row contiguously.
 #include "msda_common.cuh"
+
+// tuning knobs (compile-time): points whose corner loads are in flight together, and the
+// CTAs per SM the register allocation is held to
+#ifndef MSDA_FWD_UNROLL
+#define MSDA_FWD_UNROLL 2
+#endif
+#ifndef MSDA_FWD_MIN_CTAS
+#define MSDA_FWD_MIN_CTAS 4
+#endif
 
 namespace msda_b200 {
 
 namespace {
 
 template <typename T, bool SOFTMAX>
-__global__ void __launch_bounds__(256, 4) forward_kernel(const Params p) {
+__global__ void __launch_bounds__(256, MSDA_FWD_MIN_CTAS) forward_kernel(const Params p) {
     using VT = VecTraits<T>;
     constexpr int V = VT::kVec;
     constexpr int NV2 = V / 2;
+    constexpr int kUnroll = MSDA_FWD_UNROLL;
     extern __shared__ uint4 smem[];
     __shared__ LevelTable lt;
 
@@ -34,13 +45,14 @@ __global__ void __launch_bounds__(256, 4) forward_kernel(const Params p) {
     const int lph = 1 << p.lph_log2;
     const int ppw = 32 >> p.lph_log2;          // pairs per warp (group size)
     const int PC = p.point_chunk;
+    const int DS = 2 * PC + 1;                 // uint4 stride between slots (odd: no bank conflicts)
     const int G = p.G, D = p.D, K = p.K;
     const int P = p.L * K;
     const int GD = G * D;
     const float inv_K = 1.f / (float)K;
 
-    uint4 *desc = smem + (size_t)warp * (kDescPerWarp * 2);                 // [slot][PC][2]
-    float2 *stats = reinterpret_cast<float2 *>(smem + (size_t)nwarps * (kDescPerWarp * 2)) +
+    uint4 *desc = smem + (size_t)warp * kDescWarpVec;                 // [slot][PC][2]
+    float2 *stats = reinterpret_cast<float2 *>(smem + (size_t)nwarps * kDescWarpVec) +
                     warp * 32;                                              // softmax only
 
     load_level_table(lt, p);
@@ -89,35 +101,42 @@ __global__ void __launch_bounds__(256, 4) forward_kernel(const Params p) {
                     }
                     const int l = (int)(((float)pt + 0.5f) * inv_K);  // pt / K
                     const PointGeom geo = locate(xy.x, xy.y, lt.H[l], lt.W[l], lt.start[l], GD);
+                    // A corner outside the level keeps weight 0 and is pointed at the nearest
+                    // pixel inside it, so the gather needs no predicates; a skipped point
+                    // (geo.r0 = geo.c0 = 0, all weights 0) reads pixel (0, 0) of its level.
+                    const int H = lt.H[l], W = lt.W[l];
+                    const int ra = max(geo.r0, 0), rb = min(geo.r0 + 1, H - 1);
+                    const int ca = max(geo.c0, 0), cb = min(geo.c0 + 1, W - 1);
+                    const int row_a = (lt.start[l] + ra * W) * GD, row_b = (lt.start[l] + rb * W) * GD;
+                    A = make_uint4((unsigned)(row_a + ca * GD), (unsigned)(row_a + cb * GD),
+                                   (unsigned)(row_b + ca * GD), (unsigned)(row_b + cb * GD));
                     const float wr0 = 1.f - geo.fr, wc0 = 1.f - geo.fc;
-                    A = make_uint4((unsigned)geo.off00, (unsigned)geo.rowstride, geo.flags, 0u);
-                    Wt = make_uint4(__float_as_uint(a * (wr0 * wc0)),
-                                    __float_as_uint(a * (wr0 * geo.fc)),
-                                    __float_as_uint(a * (geo.fr * wc0)),
-                                    __float_as_uint(a * (geo.fr * geo.fc)));
+                    const unsigned f = geo.flags;
+                    Wt = make_uint4(__float_as_uint(f & kCorner00 ? a * (wr0 * wc0) : 0.f),
+                                    __float_as_uint(f & kCorner01 ? a * (wr0 * geo.fc) : 0.f),
+                                    __float_as_uint(f & kCorner10 ? a * (geo.fr * wc0) : 0.f),
+                                    __float_as_uint(f & kCorner11 ? a * (geo.fr * geo.fc) : 0.f));
                 }
-                desc[(sl * PC + j) * 2] = A;
-                desc[(sl * PC + j) * 2 + 1] = Wt;
+                desc[sl * DS + 2 * j] = A;
+                desc[sl * DS + 2 * j + 1] = Wt;
             }
             __syncwarp();
             // ---- gather ------------------------------------------------------------------
-            const uint4 *dp = desc + slot * PC * 2;
+            const uint4 *dp = desc + slot * DS;
             for (int ch = sub * V; ch < D; ch += lph * V) {
                 if (c0 == 0) {
 #pragma unroll
                     for (int i = 0; i < NV2; ++i) acc[i] = make_float2(0.f, 0.f);
                 }
                 const T *vc = vb + ch;
-#pragma unroll 2
+#pragma unroll kUnroll
                 for (int j = 0; j < pc; ++j) {
                     const uint4 A = dp[2 * j];
                     const uint4 Wt = dp[2 * j + 1];
-                    const unsigned flags = live ? A.z : 0u;
-                    const int o00 = (int)A.x, o10 = o00 + (int)A.y;
-                    const uint4 r0 = ldg16_if(vc + o00, flags & kCorner00);
-                    const uint4 r1 = ldg16_if(vc + (o00 + GD), flags & kCorner01);
-                    const uint4 r2 = ldg16_if(vc + o10, flags & kCorner10);
-                    const uint4 r3 = ldg16_if(vc + (o10 + GD), flags & kCorner11);
+                    const uint4 r0 = ldg16(vc + (int)A.x);
+                    const uint4 r1 = ldg16(vc + (int)A.y);
+                    const uint4 r2 = ldg16(vc + (int)A.z);
+                    const uint4 r3 = ldg16(vc + (int)A.w);
                     const uint4 raw[4] = {r0, r1, r2, r3};
                     const float w[4] = {__uint_as_float(Wt.x), __uint_as_float(Wt.y),
                                         __uint_as_float(Wt.z), __uint_as_float(Wt.w)};
@@ -154,7 +173,7 @@ cudaError_t launch_typed(const Params &p, cudaStream_t stream) {
 
 size_t forward_smem_bytes(const Params &p, bool softmax) {
     const size_t nwarps = p.threads / 32;
-    return nwarps * kDescPerWarp * 32 + (softmax ? nwarps * 32 * sizeof(float2) : 0);
+    return nwarps * kDescWarpVec * 16 + (softmax ? nwarps * 32 * sizeof(float2) : 0);
 }
 
 cudaError_t launch_forward(const Params &p, int dtype, bool softmax, cudaStream_t stream) {

@@ -247,7 +247,7 @@ def test_host_only_entry_points():
     # headline shape: bf16, 8 heads x 32 channels, 3 levels x 4 points, 4 x 21504 queries
     assert shim.launch_geometry(4, 8, 32, 21504, 3, 4, 2, 0, grid, threads, sf, sb) == 0
     assert threads.value == 256 and grid.value == 4 * 21504 // 8     # one warp per query
-    assert sf.value == 8 * 4096 and sb.value > sf.value
+    assert sf.value == 8 * (2 * 128 + 32) * 16 and sb.value > sf.value   # 8 warps of descriptors
     assert shim.scratch_bytes(4, 21504, 8, 32, 2) == 4 * 21504 * 256 * 4
     assert shim.scratch_bytes(4, 21504, 8, 32, 0) == 0
     # statuses and messages
