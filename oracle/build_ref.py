@@ -1,0 +1,84 @@
+"""TEST INFRASTRUCTURE - compile the REFERENCE's own CUDA kernels into ``oracle/_ref/``.
+
+The reference's MSDA kernels are a handful of headers plus one 25-line translation unit per
+configuration; they compile with a single ``nvcc`` call against the torch headers, without
+the reference's build system.  Sources are read where they lie in the reference checkout and
+are never copied; only the resulting ``.so`` files (git-ignored) are written, under
+``oracle/_ref/``:
+
+    msda_fp32acc.so       the reference's production configuration (float32 accumulation)
+    msda_half2atomic.so   its native 16-bit-atomics configuration
+
+Flags follow ``sources/deformops/core/configs.py:48-66`` (``--use_fast_math``, C++20, the
+half-operator undefines, ``-DDEFORMOPS_NO_FP64`` as in its ahead-of-time build).  The
+libraries are used by ``oracle/ref_cuda.py`` as the GPU-side parity oracle and speed bar.
+
+    python oracle/build_ref.py [--reference /path/to/reference]
+"""
+
+from __future__ import annotations
+
+import argparse
+import pathlib
+import shutil
+import subprocess
+import sys
+
+HERE = pathlib.Path(__file__).resolve().parent
+OUT = HERE / "_ref"
+UNITS = {
+    "msda_fp32acc": "sources/deformops/backends/cuda/msda_fp32acc.cu",
+    "msda_half2atomic": "sources/deformops/backends/cuda/experimental/msda_half2atomic.cu",
+}
+
+
+def build(reference: pathlib.Path, force: bool = False) -> list[pathlib.Path]:
+    import torch
+    from torch.utils import cpp_extension
+
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    include = reference / "sources/deformops/backends/cuda/include"
+    torch_lib = pathlib.Path(torch.__file__).parent / "lib"
+    OUT.mkdir(exist_ok=True)
+    built = []
+    for name, rel in UNITS.items():
+        src = reference / rel
+        target = OUT / f"{name}.so"
+        if not src.exists():
+            raise FileNotFoundError(src)
+        if target.exists() and not force and target.stat().st_mtime > src.stat().st_mtime:
+            built.append(target)
+            continue
+        cmd = [
+            nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++20",
+            "--use_fast_math", "-DUSE_CUDA", "-DTORCH_TARGET_VERSION=0x020B000000000000",
+            "-DDEFORMOPS_NO_FP64", "-U__CUDA_NO_HALF_OPERATORS__",
+            "-U__CUDA_NO_HALF_CONVERSIONS__", "-U__CUDA_NO_HALF2_OPERATORS__",
+            "-Xcompiler", "-fPIC", "-shared", f"-I{include}",
+            *[f"-I{p}" for p in cpp_extension.include_paths("cuda")],
+            str(src), "-o", str(target),
+            f"-L{torch_lib}", "-ltorch", "-ltorch_cpu", "-lc10",
+            "-Xlinker", f"-rpath={torch_lib}",
+        ]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {src}:\n{res.stderr[-4000:]}")
+        built.append(target)
+    return built
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--force", action="store_true")
+    args = ap.parse_args()
+    ref = pathlib.Path(args.reference)
+    if not ref.exists():
+        print(f"reference checkout {ref} not present: nothing built", file=sys.stderr)
+        return
+    for path in build(ref, args.force):
+        print(f"{path}  {path.stat().st_size / 1e6:.1f} MB")
+
+
+if __name__ == "__main__":
+    main()

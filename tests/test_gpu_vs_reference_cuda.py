@@ -1,0 +1,77 @@
+"""GPU parity against the REFERENCE'S OWN CUDA KERNELS on the same inputs, on the same GPU.
+
+``oracle/_ref/*.so`` are the reference's kernels compiled from its sources by
+``oracle/build_ref.py``; the tests are skipped when they have not been built.  Tolerances:
+float32 output 1e-5 and gradients 1e-4 of the reference's float32 CUDA result; bf16 / f16
+1e-2 of the reference's float32 result on the same (rounded) inputs.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref_cuda
+from tests._abi import abi_backward, abi_forward, dev, to_np
+from tests._golden import rel_err
+from tests.test_gpu_parity import _stable_points
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not ref_cuda.available(), reason="oracle/_ref not built")]
+
+
+def _inputs(name, dtype, batch=None):
+    from deformops_b200.workloads import make_workload
+
+    w = make_workload(name, batch=batch)
+    t = dict(value=dev(w.value, dtype), loc=dev(w.sampling_locations, torch.float32),
+             attn=dev(w.attention_weights, dtype), logits=dev(w.attention_logits, dtype),
+             grad_out=dev(w.grad_output, dtype), shapes=dev(w.spatial_shapes),
+             starts=dev(w.level_start_index))
+    return w, t
+
+
+def _compare(t, dtype, softmax, tol_out, tol_grad):
+    attn = t["logits"] if softmax else t["attn"]
+    args = (t["value"], t["shapes"], t["starts"], t["loc"], attn)
+    out = abi_forward(*args, softmax=softmax)
+    gv, gl, ga = abi_backward(*args, t["grad_out"], softmax=softmax)
+    # the reference's float32 result on the inputs as the kernels see them
+    f32 = [x.float() if x.is_floating_point() else x for x in args]
+    r_out = ref_cuda.forward(*f32, softmax=softmax)
+    r_gv, r_gl, r_ga = ref_cuda.backward(*f32, t["grad_out"].float(), softmax=softmax)
+    keep = _stable_points(to_np(t["loc"]), to_np(t["shapes"]))[..., None]
+    errs = {"out": rel_err(to_np(out), to_np(r_out)), "grad_value": rel_err(to_np(gv), to_np(r_gv)),
+            "grad_loc": rel_err(to_np(gl) * keep, to_np(r_gl) * keep),
+            "grad_attn": rel_err(to_np(ga), to_np(r_ga))}
+    assert errs["out"] <= tol_out, errs
+    assert max(errs["grad_value"], errs["grad_loc"], errs["grad_attn"]) <= tol_grad, errs
+    return errs
+
+
+@pytest.mark.parametrize("softmax", [False, True])
+@pytest.mark.parametrize("name", ["cfg0_cpu_fp32", "cfg3_detr_enc_fp32"])
+def test_fp32_against_reference_cuda(name, softmax):
+    _, t = _inputs(name, torch.float32)
+    _compare(t, torch.float32, softmax, 1e-5, 1e-4)
+
+
+@pytest.mark.parametrize("name,dtype", [
+    ("cfg1_m2f_512_bf16", torch.bfloat16), ("cfg2_m2f_1024_bf16", torch.bfloat16),
+    ("cfg3_detr_enc_fp16", torch.float16), ("cfg3_detr_dec_fp16", torch.float16),
+])
+def test_16bit_against_reference_cuda_fp32_result(name, dtype):
+    _, t = _inputs(name, dtype)
+    _compare(t, dtype, False, 1e-2, 1e-2)
+
+
+def test_reference_16bit_configurations_agree_too():
+    """Sanity of the oracle itself: the reference's production (fp32acc) and native-atomic
+    (half2atomic) configurations, run in bf16, stay within its own 2e-2 tolerance."""
+    _, t = _inputs("cfg1_m2f_512_bf16", torch.bfloat16, batch=2)
+    args = (t["value"], t["shapes"], t["starts"], t["loc"], t["attn"])
+    a = ref_cuda.backward(*args, t["grad_out"], prefix="msda_fp32acc")
+    b = ref_cuda.backward(*args, t["grad_out"], prefix="msda_half2atomic")
+    for x, y in zip(a, b):
+        assert rel_err(to_np(y), to_np(x)) < 5e-2

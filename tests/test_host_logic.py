@@ -276,3 +276,27 @@ def test_error_message_is_thread_local():
     t.start()
     t.join()
     assert seen == [""] and "multiple of 8" in shim.last_error()
+
+
+def test_register_into_reference_registry():
+    """With the reference checkout importable, the adapter becomes its Backend.CUDA."""
+    ref_sources = pathlib.Path("/root/reference/sources")
+    if not ref_sources.exists():
+        pytest.skip("reference checkout not present on this machine")
+    code = (
+        "import sys; sys.path.insert(0, %r)\n"
+        "import torch\n"
+        "from deformops_b200.integration import register_into_deformops, supports\n"
+        "ref = register_into_deformops()\n"
+        "from deformops.registry import Backend\n"
+        "from deformops.registry.msda import MSDAContext, Method\n"
+        "ctx = MSDAContext(device=torch.device('cuda', 0), num_levels=3, num_heads=8, num_points=4,\n"
+        "                  dtype=torch.bfloat16, sm_version=(10, 0), is_training=True, num_queries=5,\n"
+        "                  method=Method.LINEAR, head_dim=32)\n"
+        "assert supports(ctx)\n"
+        "import dataclasses\n"
+        "assert not supports(dataclasses.replace(ctx, sm_version=(9, 0)))\n"
+        "print(ref.load(Backend.CUDA))\n" % str(ref_sources))
+    res = subprocess.run([sys.executable, "-c", code], cwd=ROOT, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert "libmsda_b200.so" in res.stdout
