@@ -209,7 +209,7 @@ int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
     p.grad_loc = grad_loc;
     p.grad_attn = grad_attn;
     p.scratch = use_scratch ? static_cast<float *>(scratch) : nullptr;
-    p.scratch_adds = scratch_adds > 0 ? scratch_adds : (dtype == MSDA_B200_BF16 ? 32 : 512);
+    p.scratch_adds = scratch_adds > 0 ? scratch_adds : (dtype == MSDA_B200_BF16 ? 24 : 512);
 
     DeviceGuard guard(device);
     if (guard.err != cudaSuccess) return cuda_fail(guard.err, "backward: selecting the device");

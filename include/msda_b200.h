@@ -81,7 +81,7 @@ int msda_b200_forward(const void *value, const int64_t *spatial_shapes,
  * NULL it must hold msda_b200_backward_scratch_bytes(...) bytes (a float32 image of
  * grad_value; only the rows of the levels that use it are touched).  A level then
  * accumulates in float32 when its expected additions per element, 4*K*Q / (H*W), exceed
- * `scratch_adds`; pass 0 for the library default (32 for bf16, 512 for f16).  Such levels
+ * `scratch_adds`; pass 0 for the library default (24 for bf16, 512 for f16).  Such levels
  * are converted to `dtype` at the end of the call.  With scratch == NULL every level uses
  * direct 16-bit reductions (fastest, least accurate).  Ignored for float32.
  *
