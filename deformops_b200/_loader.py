@@ -41,7 +41,7 @@ class Shim:
     #: every symbol ``include/msda_b200.h`` declares
     SYMBOLS = ("msda_b200_abi_version", "msda_b200_last_error", "msda_b200_forward",
                "msda_b200_backward", "msda_b200_backward_scratch_bytes",
-               "msda_b200_launch_geometry")
+               "msda_b200_backward_static_scratch", "msda_b200_launch_geometry")
 
     def __init__(self, path: str):
         self.path = path
@@ -63,6 +63,10 @@ class Shim:
         self.scratch_bytes = self.lib.msda_b200_backward_scratch_bytes
         self.scratch_bytes.restype = _i64
         self.scratch_bytes.argtypes = [_i64] * 4 + [_int]
+        self.backward_static_scratch = self.lib.msda_b200_backward_static_scratch
+        self.backward_static_scratch.restype = _int
+        self.backward_static_scratch.argtypes = ([_vp] * 9 + [_i64] + [_i64] * 7
+                                                 + [_int, _int, _int, _vp])
         self.launch_geometry = self.lib.msda_b200_launch_geometry
         self.launch_geometry.restype = _int
         self.launch_geometry.argtypes = [_i64] * 6 + [_int, _int, ctypes.POINTER(_i64),

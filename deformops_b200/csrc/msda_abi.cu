@@ -110,6 +110,10 @@ int cuda_fail(cudaError_t e, const char *what) {
 
 }  // namespace
 
+namespace msda_b200 {
+int set_last_error(int status, const char *message) { return fail(status, "%s", message); }
+}  // namespace msda_b200
+
 extern "C" {
 
 int msda_b200_abi_version(void) { return MSDA_B200_ABI_VERSION; }

@@ -293,4 +293,8 @@ cudaError_t launch_finalize_grad_value(const Params &p, int dtype, cudaStream_t 
 size_t forward_smem_bytes(const Params &p, bool softmax);
 size_t backward_smem_bytes(const Params &p, bool softmax);
 
+// records `message` as the calling thread's last error (what msda_b200_last_error returns)
+// and hands `status` back; defined in msda_abi.cu next to the buffer it writes
+int set_last_error(int status, const char *message);
+
 }  // namespace msda_b200

@@ -108,6 +108,29 @@ int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
 int64_t msda_b200_backward_scratch_bytes(int64_t B, int64_t S, int64_t G, int64_t D, int dtype);
 
 /*
+ * Backward for callers that cannot allocate device memory (a runtime that handed all of it
+ * out at start-up and forbids cudaMalloc afterwards, a plugin running inside someone else's
+ * step, a C program without a caching allocator).  Same results as msda_b200_backward with a
+ * scratch buffer, but the float32 accumulator is a fixed 32 MiB array inside the library
+ * (8 Mi floats): a GPU that uses this entry point holds it until the process exits.
+ *   - B*S*G*D above 8 Mi elements (16-bit dtypes) returns MSDA_B200_UNSUPPORTED.
+ *   - No cudaMalloc / cudaFree / allocating library call is made.
+ *   - The first call on a device looks the array's address up (cudaGetSymbolAddress); make
+ *     that first call outside any stream capture.
+ *   - Every call reuses the one array, which still holds the previous call's sums; each call
+ *     clears the rows it adds into.  Calls that overlap on the GPU race: serialise them.
+ *   - grad_value is always cleared (there is no accumulate mode here).
+ * This entry point has no counterpart in the reference.
+ */
+int msda_b200_backward_static_scratch(const void *value, const int64_t *spatial_shapes,
+                                      const int64_t *level_start_index, const float *loc,
+                                      const void *attn, const void *grad_out, void *grad_value,
+                                      float *grad_loc, void *grad_attn, int64_t scratch_adds,
+                                      int64_t B, int64_t S, int64_t G, int64_t D, int64_t Q,
+                                      int64_t L, int64_t K, int dtype, int apply_softmax,
+                                      int device, void *stream);
+
+/*
  * Launch geometry the library would use for a shape, for harnesses that count launches
  * or size grids: number of CTAs, threads per CTA and dynamic shared memory of the forward
  * (*_fwd) and backward (*_bwd) kernels.  Pure function of its arguments.
