@@ -19,7 +19,7 @@ from .core.errors import KernelBuildError, KernelUnavailableError
 
 __all__ = ["ABI_VERSION", "Shim", "library_path", "load_library", "loaded"]
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 _lock = threading.Lock()
 _shim: "Shim | None" = None

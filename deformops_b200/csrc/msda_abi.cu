@@ -123,7 +123,7 @@ const char *msda_b200_last_error(void) { return g_error; }
 int64_t msda_b200_backward_scratch_bytes(int64_t B, int64_t S, int64_t G, int64_t D, int dtype) {
     if (dtype != MSDA_B200_F16 && dtype != MSDA_B200_BF16) return 0;
     if (B <= 0 || S <= 0 || G <= 0 || D <= 0) return 0;
-    return B * S * G * D * (int64_t)sizeof(float);
+    return B * S * G * D * (int64_t)(2 * msda_b200::kScratchImages);
 }
 
 int msda_b200_launch_geometry(int64_t B, int64_t G, int64_t D, int64_t Q, int64_t L, int64_t K,
@@ -213,7 +213,7 @@ int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
     p.grad_loc = grad_loc;
     p.grad_attn = grad_attn;
     p.scratch = use_scratch ? static_cast<float *>(scratch) : nullptr;
-    p.scratch_adds = scratch_adds > 0 ? scratch_adds : (dtype == MSDA_B200_BF16 ? 24 : 512);
+    p.scratch_adds = scratch_adds > 0 ? scratch_adds : (dtype == MSDA_B200_BF16 ? 12 : 256);
 
     DeviceGuard guard(device);
     if (guard.err != cudaSuccess) return cuda_fail(guard.err, "backward: selecting the device");

@@ -21,10 +21,11 @@
 //
 // Accuracy of 16-bit grad_value.  A coarse pyramid level receives hundreds of additions
 // per element; summing those in bf16 loses about sqrt(n) * 2^-9 of the result.  Levels
-// whose expected additions per element, 4*K*Q / (H*W), exceed `scratch_adds` therefore
-// accumulate in a float32 scratch with red.global.add.v4.f32 and are converted once by
-// finalize_kernel; the fine levels, which hold most of the bytes, keep the direct packed
-// 16-bit reductions.  prepare_kernel clears exactly the rows each path adds into.
+// whose expected additions per element, 4*K*Q / (H*W), exceed `scratch_adds` are therefore
+// given several replicas in a caller-provided scratch (plan_replicas in msda_common.cuh):
+// every point adds into one replica, chosen by (query + point) mod R, with the same packed
+// 16-bit reduction as everywhere else, and finalize_kernel sums the replicas in float32.
+// prepare_kernel clears exactly what the backward kernel adds into.
 #include "msda_common.cuh"
 
 namespace msda_b200 {
@@ -91,6 +92,8 @@ __global__ void __launch_bounds__(256, 3) backward_kernel(const Params p) {
 
     load_level_table(lt, p);
     __syncthreads();
+    if (threadIdx.x == 0) plan_replicas(lt, p);
+    __syncthreads();
 
     const int64_t total_pairs = p.B * p.Q * G;
     const int slot = lane >> p.lph_log2;
@@ -100,6 +103,7 @@ __global__ void __launch_bounds__(256, 3) backward_kernel(const Params p) {
     const T *grad_out = reinterpret_cast<const T *>(p.grad_out);
     const float2 *loc2 = reinterpret_cast<const float2 *>(p.loc);
     T *grad_value = reinterpret_cast<T *>(p.grad_value);
+    T *scratch = reinterpret_cast<T *>(p.scratch);
 
     for (int64_t group = (int64_t)blockIdx.x * nwarps + warp; group < p.num_groups;
          group += (int64_t)gridDim.x * nwarps) {
@@ -115,6 +119,7 @@ __global__ void __launch_bounds__(256, 3) backward_kernel(const Params p) {
         const int g = (int)(my_pair - bq * G);
         const int64_t b = bq / p.Q;
         const int64_t sample = (b * p.S * G + g) * (int64_t)D;
+        const int64_t scratch_sample = b * (int64_t)lt.scratch_sample_elems + g * D;
 
         for (int c0 = 0; c0 < P; c0 += PC) {
             const int pc = min(PC, P - c0);
@@ -138,9 +143,16 @@ __global__ void __launch_bounds__(256, 3) backward_kernel(const Params p) {
                     const PointGeom geo = locate(xy.x, xy.y, lt.H[l], lt.W[l], lt.start[l], GD);
                     // a skipped point contributes exact zeros whatever its weight holds
                     const float au = (geo.flags & kInside) ? a : 0.f;
-                    const unsigned flags = geo.flags | (lt.scratch[l] ? kUseScratch : 0u);
-                    A = make_uint4((unsigned)geo.off00, (unsigned)geo.rowstride, flags,
-                                   __float_as_uint(au));
+                    unsigned flags = geo.flags | ((unsigned)l << kLevelShift);
+                    unsigned red_off = (unsigned)geo.off00;         // direct: same place as value
+                    if (lt.rep[l] > 0) {
+                        // spread the additions of a coarse level over its replicas
+                        const unsigned r = (unsigned)((pair0 + sl) / G + pt) % (unsigned)lt.rep[l];
+                        red_off = lt.rep_base[l] + r * lt.level_elems[l] +
+                                  (unsigned)((geo.r0 * lt.W[l] + geo.c0) * GD);
+                        flags |= kUseScratch;
+                    }
+                    A = make_uint4((unsigned)geo.off00, red_off, flags, __float_as_uint(au));
                     Fr = make_uint4(__float_as_uint(geo.fr), __float_as_uint(geo.fc),
                                     __float_as_uint(au * geo.Wf), __float_as_uint(au * geo.Hf));
                 }
@@ -161,18 +173,26 @@ __global__ void __launch_bounds__(256, 3) backward_kernel(const Params p) {
                                    : make_uint4(0, 0, 0, 0), go);
                 const T *vc = value + sample + ch;
                 T *gc = grad_value + sample + ch;
-                float *sc = p.scratch + sample + ch;
+                T *sc = scratch + scratch_sample + ch;
 #pragma unroll 2
                 for (int j = 0; j < pc; ++j) {
                     const uint4 A = dp[2 * j];
                     const uint4 Fr = dp[2 * j + 1];
-                    const unsigned flags = on_lane ? A.z : 0u;
+                    const unsigned flags_all = A.z;
+                    const unsigned flags = on_lane ? flags_all : 0u;
                     const float a = __uint_as_float(A.w);
                     const float fr = __uint_as_float(Fr.x), fc = __uint_as_float(Fr.y);
                     const float wr0 = 1.f - fr, wc0 = 1.f - fc;
                     const float w[4] = {wr0 * wc0, wr0 * fc, fr * wc0, fr * fc};
-                    const int o00 = (int)A.x, o10 = o00 + (int)A.y;
+                    const int rs = lt.rowstride[flags_all >> kLevelShift];
+                    const int o00 = (int)A.x, o10 = o00 + rs;
                     const int off[4] = {o00, o00 + GD, o10, o10 + GD};
+                    // where the reductions go: grad_value itself, or this point's replica of
+                    // its level in the scratch (32-bit unsigned offsets; the scratch of one
+                    // sample spans up to 2*S*G*D elements)
+                    const unsigned q00 = A.y, q10 = q00 + (unsigned)rs;
+                    const unsigned roff[4] = {q00, q00 + (unsigned)GD, q10, q10 + (unsigned)GD};
+                    T *rbase = (flags_all & kUseScratch) ? sc : gc;
                     uint4 raw[4];
 #pragma unroll
                     for (int c = 0; c < 4; ++c) raw[c] = ldg16_if(vc + off[c], flags & (1u << c));
@@ -191,19 +211,7 @@ __global__ void __launch_bounds__(256, 3) backward_kernel(const Params p) {
                             gv[i] = fmul2(go[i], s2);
                         }
                         dot[c] = d2.x + d2.y;
-                        const bool on = flags & (1u << c);
-                        if constexpr (V == 8) {
-                            if (flags & kUseScratch) {  // uniform over the warp: same point index
-                                if (on) {
-                                    red_add_f32x4(sc + off[c], gv[0], gv[1]);
-                                    red_add_f32x4(sc + off[c] + 4, gv[2], gv[3]);
-                                }
-                            } else {
-                                red_if<T>(gc + off[c], gv, on);
-                            }
-                        } else {
-                            red_if<T>(gc + off[c], gv, on);
-                        }
+                        red_if<T>(rbase + roff[c], gv, flags & (1u << c));
                     }
                     // derivative inside the cell [floor, floor+1); d/da = sample . grad_out
                     float gx = wr0 * (dot[1] - dot[0]) + fr * (dot[3] - dot[2]);
@@ -256,7 +264,7 @@ __global__ void __launch_bounds__(256, 3) backward_kernel(const Params p) {
     }
 }
 
-// ---- grad_value preparation and finalisation for the float32-scratch levels ------------------
+// ---- grad_value preparation and finalisation for the replica levels ----------------------------
 __device__ __forceinline__ int level_of(const LevelTable &lt, int L, int s) {
     int l = 0;
     for (int i = 1; i < L; ++i)
@@ -264,52 +272,73 @@ __device__ __forceinline__ int level_of(const LevelTable &lt, int L, int s) {
     return l;
 }
 
-// Clears, per 16-byte vector of grad_value, either the vector itself (direct levels) or the
-// matching float32 scratch elements (scratch levels, whose grad_value is written by finalize).
+// Clears what the backward kernel adds into: the grad_value rows of the direct levels and the
+// replica region of every sample's scratch (the grad_value rows of replica levels are written,
+// not added to, by finalize_kernel).
 template <typename T>
 __global__ void __launch_bounds__(256) prepare_kernel(const Params p) {
     __shared__ LevelTable lt;
     load_level_table(lt, p);
     __syncthreads();
+    if (threadIdx.x == 0) plan_replicas(lt, p);
+    __syncthreads();
     constexpr int V = VecTraits<T>::kVec;
     const int vec_per_row = p.G * p.D / V;
     const int64_t total = p.B * p.S * vec_per_row;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < total;
-         v += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (int64_t v = first; v < total; v += stride) {
         const int s = (int)((v / vec_per_row) % p.S);
-        if (lt.scratch[level_of(lt, p.L, s)]) {
-            uint4 *dst = reinterpret_cast<uint4 *>(p.scratch + v * V);
-#pragma unroll
-            for (int i = 0; i < V / 4; ++i) dst[i] = zero;
-        } else {
-            reinterpret_cast<uint4 *>(p.grad_value)[v] = zero;
-        }
+        if (lt.rep[level_of(lt, p.L, s)] == 0) reinterpret_cast<uint4 *>(p.grad_value)[v] = zero;
+    }
+    int64_t used = 0;   // replica elements per sample, contiguous from the sample's base
+    for (int l = 0; l < p.L; ++l) used += (int64_t)lt.rep[l] * lt.level_elems[l];
+    const int64_t used_vec = used / V;
+    for (int64_t v = first; v < p.B * used_vec; v += stride) {
+        const int64_t b = v / used_vec, i = v - b * used_vec;
+        reinterpret_cast<uint4 *>(reinterpret_cast<T *>(p.scratch) +
+                                  b * (int64_t)lt.scratch_sample_elems)[i] = zero;
     }
 }
 
+// Sums the replicas of every replica level in float32 and writes the level's grad_value rows.
 template <typename T>
 __global__ void __launch_bounds__(256) finalize_kernel(const Params p) {
     __shared__ LevelTable lt;
     load_level_table(lt, p);
     __syncthreads();
+    if (threadIdx.x == 0) plan_replicas(lt, p);
+    __syncthreads();
     using VT = VecTraits<T>;
     constexpr int V = VT::kVec;
-    const int vec_per_row = p.G * p.D / V;
+    constexpr int NV2 = V / 2;
+    const int GD = p.G * p.D;
+    const int vec_per_row = GD / V;
     const int64_t total = p.B * p.S * vec_per_row;
     for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < total;
          v += (int64_t)gridDim.x * blockDim.x) {
-        const int s = (int)((v / vec_per_row) % p.S);
-        if (!lt.scratch[level_of(lt, p.L, s)]) continue;
-        const float4 *src = reinterpret_cast<const float4 *>(p.scratch + v * V);
-        float2 f[V / 2];
+        const int64_t row = v / vec_per_row;
+        const int s = (int)(row % p.S);
+        const int l = level_of(lt, p.L, s);
+        const int reps = lt.rep[l];
+        if (reps == 0) continue;
+        const int64_t b = row / p.S;
+        const T *src = reinterpret_cast<const T *>(p.scratch) + b * (int64_t)lt.scratch_sample_elems +
+                       lt.rep_base[l] + (int64_t)(s - lt.start[l]) * GD + (v - row * vec_per_row) * V;
+        float2 acc[NV2];
 #pragma unroll
-        for (int i = 0; i < V / 4; ++i) {
-            const float4 t = src[i];
-            f[2 * i] = make_float2(t.x, t.y);
-            f[2 * i + 1] = make_float2(t.z, t.w);
+        for (int i = 0; i < NV2; ++i) acc[i] = make_float2(0.f, 0.f);
+        for (int r = 0; r < reps; ++r) {
+            float2 f[NV2];
+            VT::unpack(*reinterpret_cast<const uint4 *>(src + (int64_t)r * lt.level_elems[l]), f);
+#pragma unroll
+            for (int i = 0; i < NV2; ++i) {
+                acc[i].x += f[i].x;
+                acc[i].y += f[i].y;
+            }
         }
-        reinterpret_cast<uint4 *>(p.grad_value)[v] = VT::pack(f);
+        reinterpret_cast<uint4 *>(p.grad_value)[v] = VT::pack(acc);
     }
 }
 

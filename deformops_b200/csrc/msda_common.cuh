@@ -28,6 +28,7 @@
 namespace msda_b200 {
 
 constexpr int kMaxLevels = 16;           // level table kept in shared memory
+constexpr int kScratchImages = 6;        // 16-bit images of grad_value the backward scratch holds
 constexpr int kDescPerWarp = 128;        // descriptors (32 B each) a warp holds at a time
 // uint4 words of descriptor storage per warp: every slot's row is padded by one uint4 so that
 // the 8 (or fewer) slots of a warp read their 16-byte descriptor halves from distinct banks
@@ -44,8 +45,8 @@ struct Params {
     void *grad_value;       // backward only
     float *grad_loc;        // backward only
     void *grad_attn;        // backward only
-    float *scratch;         // backward only: float32 accumulator rows for the levels that use it
-    int64_t scratch_adds;   // a level uses the scratch when 4*K*Q > scratch_adds * H*W (0: never)
+    void *scratch;          // backward only: replica accumulators (element type T), or null
+    int64_t scratch_adds;   // additions per accumulator a level may see before it gets replicas
     int64_t B, S, Q;
     int G, D, L, K;
     int lph_log2;           // log2(lanes per slot)
@@ -135,12 +136,6 @@ template <> struct VecTraits<__half> {
     }
 };
 
-// four float adds into a float32 accumulator row
-__device__ __forceinline__ void red_add_f32x4(float *addr, float2 a, float2 b) {
-    asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr),
-                 "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-}
-
 // packed two-wide float32 arithmetic (sm_100): one issue slot for two lanes of work
 __device__ __forceinline__ void ffma2(float2 &acc, const float2 a, const float2 b) {
     asm("fma.rn.f32x2 %0, %1, %2, %0;"
@@ -201,23 +196,71 @@ __device__ __forceinline__ void st_stream_f2(float2 *p, float2 v) {
 struct LevelTable {
     int H[kMaxLevels];
     int W[kMaxLevels];
-    int start[kMaxLevels];     // first position of the level on the S axis
-    int scratch[kMaxLevels];   // backward: the level accumulates grad_value in float32 scratch
+    int start[kMaxLevels];          // first position of the level on the S axis
+    int rowstride[kMaxLevels];      // elements between image rows: W * G * D
+    // backward, 16-bit grad_value: replica accumulators of the coarse levels (see
+    // plan_replicas); rep[l] == 0 means the level adds straight into grad_value
+    int rep[kMaxLevels];
+    unsigned rep_base[kMaxLevels];     // first element of the level's replicas in a sample's scratch
+    unsigned level_elems[kMaxLevels];  // H * W * G * D
+    unsigned long long scratch_sample_elems;   // scratch elements (of T) reserved per sample
 };
 
-__device__ __forceinline__ bool level_uses_scratch(const Params &p, int64_t H, int64_t W) {
-    return p.scratch != nullptr && p.scratch_adds > 0 &&
-           4 * (int64_t)p.K * p.Q > p.scratch_adds * H * W;
+// Replica plan for the 16-bit backward.  A level whose elements receive more than
+// `scratch_adds` additions each - 4*K*Q / (H*W) on average - is given R copies ("replicas")
+// in the scratch so that no accumulator sees more than about `scratch_adds` of them; the
+// finalize kernel sums the copies in float32.  All reductions stay packed 16-bit, which the
+// L2 reduction units process about three times faster per element than float32.  Splitting a
+// sum over R accumulators divides its rounding error by about R (each accumulator is R times
+// smaller and sees R times fewer additions).  The scratch holds kScratchImages * S*G*D
+// elements per sample; if the plan does not fit, the per-replica budget of additions is raised
+// until it does.  Every kernel of
+// one backward call derives the same plan from the same level table.
+__device__ inline void plan_replicas(LevelTable &t, const Params &p) {
+    const long long GD = (long long)p.G * p.D;
+    // per sample the scratch holds kScratchImages 16-bit images of grad_value; replica offsets
+    // are 32-bit, so a plan never uses more than 2^32 - 1 elements of it
+    const long long reserved = (long long)kScratchImages * p.S * GD;
+    const long long budget = reserved < 0xffffffffll ? reserved : 0xffffffffll;
+    t.scratch_sample_elems = (unsigned long long)reserved;
+    for (int l = 0; l < p.L; ++l) {
+        t.rep[l] = 0;
+        t.rep_base[l] = 0;
+    }
+    if (p.scratch == nullptr || p.scratch_adds <= 0) return;
+    const long long n4 = 4ll * p.K * p.Q;
+    long long adds = p.scratch_adds;
+    for (int iter = 0; iter < 24; ++iter) {
+        long long total = 0;
+        for (int l = 0; l < p.L; ++l) {
+            const long long hw = (long long)t.H[l] * t.W[l];
+            const long long r = n4 > adds * hw ? (n4 + adds * hw - 1) / (adds * hw) : 0;
+            t.rep[l] = (int)r;
+            total += r * hw * GD;
+        }
+        if (total <= budget) {
+            unsigned base = 0;
+            for (int l = 0; l < p.L; ++l) {
+                t.rep_base[l] = base;
+                base += (unsigned)t.rep[l] * t.level_elems[l];
+            }
+            return;
+        }
+        const long long grow = (total + budget - 1) / budget;
+        adds = adds * (grow > 1 ? grow : 2);
+    }
+    for (int l = 0; l < p.L; ++l) t.rep[l] = 0;   // cannot happen for sane tables: all direct
 }
 
 __device__ __forceinline__ void load_level_table(LevelTable &t, const Params &p) {
     if (threadIdx.x < p.L) {
-        const int64_t H = p.spatial_shapes[2 * threadIdx.x];
-        const int64_t W = p.spatial_shapes[2 * threadIdx.x + 1];
-        t.H[threadIdx.x] = (int)H;
-        t.W[threadIdx.x] = (int)W;
+        const int H = (int)p.spatial_shapes[2 * threadIdx.x];
+        const int W = (int)p.spatial_shapes[2 * threadIdx.x + 1];
+        t.H[threadIdx.x] = H;
+        t.W[threadIdx.x] = W;
         t.start[threadIdx.x] = (int)p.level_start_index[threadIdx.x];
-        t.scratch[threadIdx.x] = level_uses_scratch(p, H, W) ? 1 : 0;
+        t.rowstride[threadIdx.x] = W * p.G * p.D;
+        t.level_elems[threadIdx.x] = (unsigned)H * (unsigned)W * (unsigned)(p.G * p.D);
     }
 }
 
@@ -227,7 +270,8 @@ __device__ __forceinline__ void load_level_table(LevelTable &t, const Params &p)
 enum : unsigned {
     kCorner00 = 1u, kCorner01 = 2u, kCorner10 = 4u, kCorner11 = 8u,  // corner inside the level
     kInside = 16u,       // point passes -1 <= pixel < size on both axes (NaN / inf fail)
-    kUseScratch = 32u,   // backward: accumulate this point's grad_value in float32 scratch
+    kUseScratch = 32u,   // backward: this point's grad_value goes to a scratch replica
+    kLevelShift = 8,     // bits 8.. of the flags word carry the level index (backward)
 };
 
 struct PointGeom {

@@ -5,13 +5,14 @@
 // cudaMalloc afterwards (the call synchronises the whole device and can fail late), a plugin
 // that runs inside somebody else's step where any allocator call is off limits, or a plain C
 // caller with no caching allocator at hand.  For a 16-bit backward they still need the
-// float32 accumulator that keeps the coarse pyramid levels accurate.  This entry point
+// scratch accumulators that keep the coarse pyramid levels accurate.  This entry point
 // brings its own: a fixed array that lives in the library's device image.
 //
 //  * The array is `kStaticScratchFloats` floats (32 MiB).  Every GPU on which this entry
 //    point is used holds those 32 MiB from then until the process exits.
-//  * Shapes with B*S*G*D above that many elements are refused with MSDA_B200_UNSUPPORTED;
-//    use msda_b200_backward with a caller-owned scratch for those.
+//  * The backward wants 12 bytes of scratch per grad_value element, so shapes with B*S*G*D
+//    above 2 796 202 elements are refused with MSDA_B200_UNSUPPORTED; use msda_b200_backward
+//    with a caller-owned scratch for those.
 //  * Nothing is allocated or freed, here or further down: no cudaMalloc, no cudaFree, no
 //    library routine that allocates.  Inputs and outputs are still the caller's buffers.
 //  * The first call on a device looks up the array's device address
@@ -69,9 +70,10 @@ extern "C" int msda_b200_backward_static_scratch(
     const int64_t need = msda_b200_backward_scratch_bytes(B, S, G, D, dtype);
     if (need > kStaticScratchFloats * (int64_t)sizeof(float)) {
         snprintf(message, sizeof(message),
-                 "backward_static_scratch: B*S*G*D = %lld elements exceed the built-in scratch of "
-                 "%lld floats (32 MiB); call msda_b200_backward with a scratch buffer of your own",
-                 (long long)(B * S * G * D), (long long)kStaticScratchFloats);
+                 "backward_static_scratch: B*S*G*D = %lld elements need %lld bytes and exceed the "
+                 "built-in scratch of 32 MiB; call msda_b200_backward with a scratch buffer of "
+                 "your own",
+                 (long long)(B * S * G * D), (long long)need);
         return msda_b200::set_last_error(MSDA_B200_UNSUPPORTED, message);
     }
     float *scratch = nullptr;

@@ -36,7 +36,7 @@
 extern "C" {
 #endif
 
-#define MSDA_B200_ABI_VERSION 2
+#define MSDA_B200_ABI_VERSION 3
 
 enum msda_b200_dtype { MSDA_B200_F32 = 0, MSDA_B200_F16 = 1, MSDA_B200_BF16 = 2 };
 
@@ -76,22 +76,23 @@ int msda_b200_forward(const void *value, const int64_t *spatial_shapes,
  * exact zeros).  If zero_grad_value != 0 the call first clears grad_value on `stream`;
  * pass 0 to accumulate into a buffer the caller prepared (scratch must then be NULL).
  *
- * scratch / scratch_adds (16-bit dtypes only): summing hundreds of contributions per
- * element in f16/bf16 loses accuracy on coarse pyramid levels.  When `scratch` is not
- * NULL it must hold msda_b200_backward_scratch_bytes(...) bytes (a float32 image of
- * grad_value; only the rows of the levels that use it are touched).  A level then
- * accumulates in float32 when its expected additions per element, 4*K*Q / (H*W), exceed
- * `scratch_adds`; pass 0 for the library default (24 for bf16, 512 for f16).  Such levels
- * are converted to `dtype` at the end of the call.  With scratch == NULL every level uses
- * direct 16-bit reductions (fastest, least accurate).  Ignored for float32.
+ * scratch / scratch_adds (16-bit dtypes only): summing many contributions per element in
+ * f16/bf16 loses accuracy (about sqrt(n) * 2^-9 for bf16), and a coarse pyramid level
+ * receives hundreds.  When `scratch` is not NULL it must hold
+ * msda_b200_backward_scratch_bytes(...) bytes.  A level whose elements receive more than
+ * `scratch_adds` additions on average, 4*K*Q / (H*W), is then spread over several replica
+ * accumulators in the scratch (same packed 16-bit reductions), which are summed in float32
+ * at the end of the call; pass 0 for the library default (12 for bf16, 256 for f16).  Only
+ * the part of the scratch the replicas need is touched.  With scratch == NULL every level
+ * adds straight into grad_value (fastest, least accurate).  Ignored for float32.
  *
  * Replaces: boxed op `<prefix>_backward` / `<prefix>_softmax_backward`
  *   sources/deformops/backends/cuda/include/msda_boxed.cuh:32-53
  *   sources/deformops/backends/cuda/include/msda_launch.cuh:141-275 (backward_cuda)
  *   schema sources/deformops/backends/cuda/_schema.py:24-29
  * Differences: gradients and scratch are caller-allocated; grad_attn is produced directly
- * in `dtype`; the float32 accumulator covers only the levels that need it instead of the
- * whole tensor (msda_launch.cuh:188-197, 263-273 upcast, clear and cast back everything).
+ * in `dtype`; accuracy comes from 16-bit replica accumulators instead of a float32 copy of
+ * the whole tensor (msda_launch.cuh:188-197, 263-273 upcast, clear and cast back everything).
  */
 int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
                        const int64_t *level_start_index, const float *loc, const void *attn,
@@ -101,8 +102,8 @@ int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
                        int apply_softmax, int zero_grad_value, int device, void *stream);
 
 /*
- * Bytes of float32 scratch msda_b200_backward can use for a shape: B*S*G*D*4 for the
- * 16-bit dtypes, 0 for float32.
+ * Bytes of scratch msda_b200_backward can use for a shape: six 16-bit images of grad_value
+ * (B*S*G*D*12) for the 16-bit dtypes, 0 for float32.
  * Replaces: the `new_zeros` float32 grad_value of msda_launch.cuh:188-197.
  */
 int64_t msda_b200_backward_scratch_bytes(int64_t B, int64_t S, int64_t G, int64_t D, int dtype);
@@ -111,9 +112,10 @@ int64_t msda_b200_backward_scratch_bytes(int64_t B, int64_t S, int64_t G, int64_
  * Backward for callers that cannot allocate device memory (a runtime that handed all of it
  * out at start-up and forbids cudaMalloc afterwards, a plugin running inside someone else's
  * step, a C program without a caching allocator).  Same results as msda_b200_backward with a
- * scratch buffer, but the float32 accumulator is a fixed 32 MiB array inside the library
- * (8 Mi floats): a GPU that uses this entry point holds it until the process exits.
- *   - B*S*G*D above 8 Mi elements (16-bit dtypes) returns MSDA_B200_UNSUPPORTED.
+ * scratch buffer, but the scratch is a fixed 32 MiB array inside the library: a GPU that
+ * uses this entry point holds it until the process exits.
+ *   - B*S*G*D above 2 796 202 elements (32 MiB / 12 bytes each; 16-bit dtypes) returns
+ *     MSDA_B200_UNSUPPORTED.
  *   - No cudaMalloc / cudaFree / allocating library call is made.
  *   - The first call on a device looks the array's address up (cudaGetSymbolAddress); make
  *     that first call outside any stream capture.

@@ -3,7 +3,7 @@
 It exists for hosts that cannot hand the library a scratch buffer when they call it - a
 serving or training runtime that split up all device memory at start-up and forbids
 ``cudaMalloc`` afterwards, a plugin running inside another framework's step, a C program with
-no caching allocator - and keeps its float32 accumulator in a fixed 32 MiB array inside the
+no caching allocator - and keeps its scratch accumulators in a fixed 32 MiB array inside the
 library instead.  The test calls it through the C ABI twice in a row, with different inputs,
 and checks both results against the ordinary entry point (caller-owned scratch): the second
 call must not see anything the first one left in the shared array.  This file is collected
@@ -21,15 +21,15 @@ from tests._abi import abi_backward, dev, dims
 
 pytestmark = pytest.mark.gpu
 
-# same tolerances as tests/test_gpu_parity.py for 16-bit gradients (max|a-b| / max|b|); the
-# two entry points run the same kernels, so only the order of the atomic sums differs
-TOL_GRAD_VALUE = 1e-2
+# max|a-b| / max|b| between the two entry points.  They run the same kernels on the same plan,
+# so they differ only by the order of the 16-bit atomic additions: f16 well inside 1e-2; bf16
+# gets the 2e-2 that tests/test_gpu_parity.py grants 16-bit runs that are decided by a few
+# elements (two independently ordered bf16 sums are compared here, not one against the truth).
+TOL_GRAD_VALUE = {torch.float16: 1e-2, torch.bfloat16: 2e-2}
 
-
-# Every level accumulates in float32 in this comparison (threshold of one addition per element),
-# on both entry points: the whole built-in array is exercised, and the two results then differ
-# by float32 summation order only, never by the order of 16-bit roundings.
-SCRATCH_ADDS = 1
+# 0 = the library's default number of additions an accumulator may see before its level is
+# spread over replicas in the scratch; with this workload both coarse levels use the scratch
+SCRATCH_ADDS = 0
 
 
 def _static_backward(value, shapes, starts, loc, attn, grad_out, *, softmax=False):
@@ -52,7 +52,7 @@ def _static_backward(value, shapes, starts, loc, attn, grad_out, *, softmax=Fals
 def _workload(first_sample, dtype):
     from deformops_b200.workloads import make_workload
 
-    # 2 x 5376 x 8 x 32 = 2.75 M elements: inside the 8 Mi-float array
+    # 2 x 5376 x 8 x 32 = 2.75 M elements x 12 bytes of scratch: just inside the 32 MiB array
     w = make_workload("cfg1_m2f_512_bf16", batch=2, first_sample=first_sample)
     return (dev(w.value, dtype), dev(w.spatial_shapes), dev(w.level_start_index),
             dev(w.sampling_locations, torch.float32), dev(w.attention_weights, dtype),
@@ -71,7 +71,7 @@ def test_two_calls_in_a_row_match_the_caller_scratch_entry_point(dtype):
         assert torch.equal(ga, e_ga), f"grad_attn differs on call {call}"
         assert torch.isfinite(gv).all()
         err = (gv.float() - e_gv.float()).abs().max() / e_gv.float().abs().max()
-        assert err.item() <= TOL_GRAD_VALUE, f"grad_value off by {err.item():.3e} on call {call}"
+        assert err.item() <= TOL_GRAD_VALUE[dtype], f"grad_value off by {err.item():.3e} on call {call}"
 
 
 def test_float32_needs_no_scratch_and_softmax_works():
@@ -92,4 +92,4 @@ def test_shapes_beyond_the_built_in_array_are_refused():
             dev(w.sampling_locations), dev(w.attention_weights), dev(w.grad_output))
     status, message, _ = _static_backward(*args)
     assert status == -2
-    assert "exceed the built-in scratch" in message and "msda_b200_backward" in message
+    assert "exceed the built-in scratch" in message.replace("\n", " ") and "msda_b200_backward" in message
