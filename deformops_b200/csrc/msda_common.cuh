@@ -337,6 +337,25 @@ cudaError_t launch_finalize_grad_value(const Params &p, int dtype, cudaStream_t 
 size_t forward_smem_bytes(const Params &p, bool softmax);
 size_t backward_smem_bytes(const Params &p, bool softmax);
 
+// L2 access-policy window over the value tensor (msda_l2_window.cu): fills `attr` and returns
+// 1 when the opt-in feature is on, else 0
+int l2_window_attribute(const void *base, size_t bytes, cudaLaunchAttribute *attr);
+
+// launches `kernel(p)` with the value tensor's L2 window attached when there is one
+template <typename Kernel>
+inline cudaError_t launch_with_value_window(Kernel kernel, const Params &p, size_t value_bytes,
+                                            size_t smem, cudaStream_t stream) {
+    cudaLaunchAttribute attr[1];
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.grid);
+    cfg.blockDim = dim3((unsigned)p.threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = (unsigned)l2_window_attribute(p.value, value_bytes, attr);
+    return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 // records `message` as the calling thread's last error (what msda_b200_last_error returns)
 // and hands `status` back; defined in msda_abi.cu next to the buffer it writes
 int set_last_error(int status, const char *message);

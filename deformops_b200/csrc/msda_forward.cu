@@ -165,8 +165,8 @@ cudaError_t launch_typed(const Params &p, cudaStream_t stream) {
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    kernel<<<p.grid, p.threads, smem, stream>>>(p);
-    return cudaGetLastError();
+    const size_t value_bytes = (size_t)(p.B * p.S) * p.G * p.D * sizeof(T);
+    return launch_with_value_window(kernel, p, value_bytes, smem, stream);
 }
 
 }  // namespace
