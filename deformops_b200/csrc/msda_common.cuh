@@ -206,16 +206,18 @@ struct LevelTable {
     unsigned long long scratch_sample_elems;   // scratch elements (of T) reserved per sample
 };
 
-// Replica plan for the 16-bit backward.  A level whose elements receive more than
-// `scratch_adds` additions each - 4*K*Q / (H*W) on average - is given R copies ("replicas")
-// in the scratch so that no accumulator sees more than about `scratch_adds` of them; the
-// finalize kernel sums the copies in float32.  All reductions stay packed 16-bit, which the
-// L2 reduction units process about three times faster per element than float32.  Splitting a
-// sum over R accumulators divides its rounding error by about R (each accumulator is R times
-// smaller and sees R times fewer additions).  The scratch holds kScratchImages * S*G*D
-// elements per sample; if the plan does not fit, the per-replica budget of additions is raised
-// until it does.  Every kernel of
-// one backward call derives the same plan from the same level table.
+// Replica plan for the 16-bit backward.  An element of level l receives n = 4*K*Q / (H*W)
+// additions on average; summed in one 16-bit accumulator they lose about sqrt(n) ulps of the
+// result (measured on B200: 4.0e-2 of the maximum at n = 336, 0.8e-2..1.1e-2 at n = 21, bf16).
+// A level with n > scratch_adds is therefore spread over R = ceil(n / scratch_adds) replica
+// accumulators in the scratch, so that no accumulator sees more than about `scratch_adds`
+// additions; every point adds into one replica and the finalize kernel sums the replicas in
+// float32.  (The loss depends on the additions per accumulator: a rule R ~ sqrt(n) was tried
+// and measured 1.2e-2 where this one gives 6.3e-3.)  All reductions stay packed 16-bit, which
+// the L2 reduction units process about three times faster per element than float32.  The
+// scratch holds kScratchImages * S*G*D elements per sample; if the plan does not fit,
+// `scratch_adds` is raised until it does.  Every kernel of one backward call derives the same
+// plan from the same level table.
 __device__ inline void plan_replicas(LevelTable &t, const Params &p) {
     const long long GD = (long long)p.G * p.D;
     // per sample the scratch holds kScratchImages 16-bit images of grad_value; replica offsets
@@ -234,6 +236,7 @@ __device__ inline void plan_replicas(LevelTable &t, const Params &p) {
         long long total = 0;
         for (int l = 0; l < p.L; ++l) {
             const long long hw = (long long)t.H[l] * t.W[l];
+            // R = ceil(n / adds) replicas; n <= adds: the one accumulator is grad_value itself
             const long long r = n4 > adds * hw ? (n4 + adds * hw - 1) / (adds * hw) : 0;
             t.rep[l] = (int)r;
             total += r * hw * GD;

@@ -76,15 +76,16 @@ int msda_b200_forward(const void *value, const int64_t *spatial_shapes,
  * exact zeros).  If zero_grad_value != 0 the call first clears grad_value on `stream`;
  * pass 0 to accumulate into a buffer the caller prepared (scratch must then be NULL).
  *
- * scratch / scratch_adds (16-bit dtypes only): summing many contributions per element in
- * f16/bf16 loses accuracy (about sqrt(n) * 2^-9 for bf16), and a coarse pyramid level
+ * scratch / scratch_adds (16-bit dtypes only): summing n contributions per element in
+ * f16/bf16 loses about sqrt(n) ulps (2^-9 each for bf16), and a coarse pyramid level
  * receives hundreds.  When `scratch` is not NULL it must hold
  * msda_b200_backward_scratch_bytes(...) bytes.  A level whose elements receive more than
- * `scratch_adds` additions on average, 4*K*Q / (H*W), is then spread over several replica
- * accumulators in the scratch (same packed 16-bit reductions), which are summed in float32
- * at the end of the call; pass 0 for the library default (12 for bf16, 256 for f16).  Only
- * the part of the scratch the replicas need is touched.  With scratch == NULL every level
- * adds straight into grad_value (fastest, least accurate).  Ignored for float32.
+ * `scratch_adds` additions on average, n = 4*K*Q / (H*W), is then spread over
+ * ceil(n / scratch_adds) replica accumulators in the scratch (same packed 16-bit
+ * reductions), which are summed in float32 at the end of the call.  Pass 0 for the library
+ * default (12 for bf16, 256 for f16).  Only the part of the scratch the replicas need is
+ * touched.  With scratch == NULL every level adds straight into grad_value (fastest, least
+ * accurate).  Ignored for float32.
  *
  * Replaces: boxed op `<prefix>_backward` / `<prefix>_softmax_backward`
  *   sources/deformops/backends/cuda/include/msda_boxed.cuh:32-53
