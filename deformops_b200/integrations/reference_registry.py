@@ -13,10 +13,10 @@ from __future__ import annotations
 
 from typing import Any
 
-from ._loader import load_library
-from .core.runtime import Method, resolve_method
-from .registry.msda import forward as _forward
-from .registry.msda import unsupported_reason
+from .._loader import load_library
+from ..core.runtime import Method, resolve_method
+from ..registry.msda import forward as _forward
+from ..registry.msda import unsupported_reason
 
 __all__ = ["msda_b200_adapter", "register_into_deformops", "supports"]
 

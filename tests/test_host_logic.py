@@ -286,7 +286,7 @@ def test_register_into_reference_registry():
     code = (
         "import sys; sys.path.insert(0, %r)\n"
         "import torch\n"
-        "from deformops_b200.integration import register_into_deformops, supports\n"
+        "from deformops_b200.integrations.reference_registry import register_into_deformops, supports\n"
         "ref = register_into_deformops()\n"
         "from deformops.registry import Backend\n"
         "from deformops.registry.msda import MSDAContext, Method\n"
