@@ -32,34 +32,6 @@ namespace msda_b200 {
 
 namespace {
 
-// predicated packed reductions: one instruction, no branch
-template <typename T>
-__device__ __forceinline__ void red_if(T *addr, const float2 (&g)[VecTraits<T>::kVec / 2], bool pred);
-
-template <>
-__device__ __forceinline__ void red_if<float>(float *addr, const float2 (&g)[2], bool pred) {
-    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %5, 0;\n\t"
-                 "@q red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n\t}" ::"l"(addr),
-                 "f"(g[0].x), "f"(g[0].y), "f"(g[1].x), "f"(g[1].y), "r"((unsigned)pred));
-}
-template <>
-__device__ __forceinline__ void red_if<__nv_bfloat16>(__nv_bfloat16 *addr, const float2 (&g)[4],
-                                                      bool pred) {
-    const uint4 v = VecTraits<__nv_bfloat16>::pack(g);
-    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %5, 0;\n\t"
-                 "@q red.relaxed.gpu.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};\n\t}" ::"l"(
-                     addr),
-                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"((unsigned)pred));
-}
-template <>
-__device__ __forceinline__ void red_if<__half>(__half *addr, const float2 (&g)[4], bool pred) {
-    const uint4 v = VecTraits<__half>::pack(g);
-    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %5, 0;\n\t"
-                 "@q red.relaxed.gpu.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};\n\t}" ::"l"(
-                     addr),
-                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"((unsigned)pred));
-}
-
 template <typename T, bool SOFTMAX>
 __global__ void __launch_bounds__(256, 3) backward_kernel(const Params p) {
     using VT = VecTraits<T>;

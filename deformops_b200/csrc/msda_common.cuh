@@ -136,6 +136,34 @@ template <> struct VecTraits<__half> {
     }
 };
 
+// predicated packed reductions: one instruction, no branch
+template <typename T>
+__device__ __forceinline__ void red_if(T *addr, const float2 (&g)[VecTraits<T>::kVec / 2], bool pred);
+
+template <>
+__device__ __forceinline__ void red_if<float>(float *addr, const float2 (&g)[2], bool pred) {
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %5, 0;\n\t"
+                 "@q red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n\t}" ::"l"(addr),
+                 "f"(g[0].x), "f"(g[0].y), "f"(g[1].x), "f"(g[1].y), "r"((unsigned)pred));
+}
+template <>
+__device__ __forceinline__ void red_if<__nv_bfloat16>(__nv_bfloat16 *addr, const float2 (&g)[4],
+                                                      bool pred) {
+    const uint4 v = VecTraits<__nv_bfloat16>::pack(g);
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %5, 0;\n\t"
+                 "@q red.relaxed.gpu.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};\n\t}" ::"l"(
+                     addr),
+                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"((unsigned)pred));
+}
+template <>
+__device__ __forceinline__ void red_if<__half>(__half *addr, const float2 (&g)[4], bool pred) {
+    const uint4 v = VecTraits<__half>::pack(g);
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %5, 0;\n\t"
+                 "@q red.relaxed.gpu.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};\n\t}" ::"l"(
+                     addr),
+                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"((unsigned)pred));
+}
+
 // packed two-wide float32 arithmetic (sm_100): one issue slot for two lanes of work
 __device__ __forceinline__ void ffma2(float2 &acc, const float2 a, const float2 b) {
     asm("fma.rn.f32x2 %0, %1, %2, %0;"
@@ -339,6 +367,9 @@ cudaError_t launch_prepare_grad_value(const Params &p, int dtype, cudaStream_t s
 cudaError_t launch_finalize_grad_value(const Params &p, int dtype, cudaStream_t stream);
 size_t forward_smem_bytes(const Params &p, bool softmax);
 size_t backward_smem_bytes(const Params &p, bool softmax);
+// region-tiled backward for encoder calls (msda_backward_region.cu)
+bool backward_region_eligible(const Params &p, int dtype, bool softmax);
+cudaError_t launch_backward_region(const Params &p, int dtype, bool softmax, cudaStream_t stream);
 
 // L2 access-policy window over the value tensor (msda_l2_window.cu): fills `attr` and returns
 // 1 when the opt-in feature is on, else 0
