@@ -231,12 +231,12 @@ int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
     // kernel, which pre-reduces the coarse levels in shared memory.  Off by default: it cuts
     // the L2 reduction sectors five-fold but executes 1.8x the instructions and measured
     // 1.12 ms against 0.55 ms for the generic kernel on the headline shape.
-    static const bool region_allowed = [] {
+    static const int region_mode = [] {
         const char *v = std::getenv("MSDA_B200_REGION_BACKWARD");
-        return v != nullptr && v[0] == '1';
+        return v != nullptr && (v[0] == '1' || v[0] == '2') ? v[0] - '0' : 0;
     }();
-    if (region_allowed && msda_b200::backward_region_eligible(p, dtype, apply_softmax != 0))
-        e = msda_b200::launch_backward_region(p, dtype, apply_softmax != 0, s);
+    if (region_mode && msda_b200::backward_region_eligible(p, dtype, apply_softmax != 0))
+        e = msda_b200::launch_backward_region(p, dtype, apply_softmax != 0, region_mode == 1, s);
     else
         e = msda_b200::launch_backward(p, dtype, apply_softmax != 0, s);
     if (e != cudaSuccess) return cuda_fail(e, "backward: kernel launch");

@@ -58,6 +58,7 @@ struct ItemGeom {                             // per work item
 };
 
 __device__ inline void make_region_plan(RegionPlan &rp, const LevelTable &lt, const Params &p) {
+    const int window_budget = p.region_window_ints;
     long long total = 0;
     int maxH = 1, maxW = 1;
     for (int l = 0; l < p.L; ++l) {
@@ -100,7 +101,7 @@ __device__ inline void make_region_plan(RegionPlan &rp, const LevelTable &lt, co
         const int wh = min(lt.H[best], (lt.H[best] + rp.RY - 1) / rp.RY + 1 + 2 * my);
         const int ww = min(lt.W[best], (lt.W[best] + rp.RX - 1) / rp.RX + 1 + 2 * mx);
         const int ints = wh * ww * p.D;
-        if (used + ints > kWindowInts) break;
+        if (used + ints > window_budget) break;
         rp.wh[best] = wh;
         rp.ww[best] = ww;
         rp.woff[best] = used;
@@ -175,7 +176,7 @@ __device__ __forceinline__ void window_add(const int *win_pixel, const float (&g
 }
 
 template <typename T, bool SOFTMAX>
-__global__ void __launch_bounds__(kRegionThreads, 1) backward_region_kernel(const Params p) {
+__global__ void __launch_bounds__(kRegionThreads) backward_region_kernel(const Params p) {
     using VT = VecTraits<T>;
     constexpr int V = VT::kVec;
     constexpr int NV2 = V / 2;
@@ -198,9 +199,9 @@ __global__ void __launch_bounds__(kRegionThreads, 1) backward_region_kernel(cons
 
     // shared memory: windows | per-warp descriptors | per-warp staging
     int *windows = reinterpret_cast<int *>(smem);
-    uint4 *desc = smem + kWindowInts / 4 + (size_t)warp * (ppw * DS);
+    uint4 *desc = smem + p.region_window_ints / 4 + (size_t)warp * (ppw * DS);
     const int stage_floats = backward_stage_floats(ppw, P, SOFTMAX) + 32;
-    float *stage = reinterpret_cast<float *>(smem + kWindowInts / 4 + (size_t)nwarps * (ppw * DS)) +
+    float *stage = reinterpret_cast<float *>(smem + p.region_window_ints / 4 + (size_t)nwarps * (ppw * DS)) +
                    (size_t)warp * stage_floats;
     float2 *s_stats = reinterpret_cast<float2 *>(stage);          // [32]
     float2 *s_gloc = s_stats + 32;                                // [ppw*P]
@@ -514,12 +515,12 @@ __global__ void __launch_bounds__(kRegionThreads, 1) backward_region_kernel(cons
 
 }  // namespace
 
-size_t backward_region_smem_bytes(const Params &p, bool softmax) {
-    const size_t nwarps = kRegionThreads / 32;
+size_t backward_region_smem_bytes(const Params &p, bool softmax, int threads, int window_ints) {
+    const size_t nwarps = threads / 32;
     const size_t ppw = 32 >> p.lph_log2;
     const size_t DS = 3 * p.K + 1 + (p.K & 1);
     const size_t stage_floats = backward_stage_floats((int)ppw, p.L * p.K, softmax) + 32;
-    return (size_t)kWindowInts * 4 + nwarps * (ppw * DS * 16 + stage_floats * sizeof(float));
+    return (size_t)window_ints * 4 + nwarps * (ppw * DS * 16 + stage_floats * sizeof(float));
 }
 
 // The region kernel takes encoder-shaped calls whose per-warp state fits: one channel vector
@@ -530,36 +531,39 @@ bool backward_region_eligible(const Params &p, int dtype, bool softmax) {
     if (p.Q != p.S || p.Q >= (1ll << 31) || p.D > 32 * vec || p.D % vec != 0) return false;
     if ((1 << p.lph_log2) * vec != p.D) return false;      // every lane of a slot carries channels
     if (ppw * p.K > 128 || p.D * 4 > kWindowInts) return false;
-    return backward_region_smem_bytes(p, softmax) <= 220 * 1024;
+    return backward_region_smem_bytes(p, softmax, kRegionThreads, kWindowInts) <= 220 * 1024;
 }
 
 template <typename T, bool SOFTMAX>
-static cudaError_t launch_region_typed(const Params &p, cudaStream_t stream) {
-    const size_t smem = backward_region_smem_bytes(p, SOFTMAX);
+static cudaError_t launch_region_typed(const Params &p, bool windows, cudaStream_t stream) {
+    Params q = p;
+    q.threads = windows ? kRegionThreads : 256;
+    q.region_window_ints = windows ? kWindowInts : 0;
+    const size_t smem = backward_region_smem_bytes(p, SOFTMAX, q.threads, q.region_window_ints);
     auto kernel = backward_region_kernel<T, SOFTMAX>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess)
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    Params q = p;
-    q.grid = (unsigned)sms;              // persistent: one CTA per SM walks the work items
-    q.threads = kRegionThreads;
+    // persistent CTAs walk the work items: one per SM with windows, three without
+    q.grid = (unsigned)(windows ? sms : 3 * sms);
     const size_t value_bytes = (size_t)(p.B * p.S) * p.G * p.D * sizeof(T);
     return launch_with_value_window(kernel, q, value_bytes, smem, stream);
 }
 
-cudaError_t launch_backward_region(const Params &p, int dtype, bool softmax, cudaStream_t stream) {
+cudaError_t launch_backward_region(const Params &p, int dtype, bool softmax, bool windows,
+                                   cudaStream_t stream) {
     switch (dtype) {
         case 0:
-            return softmax ? launch_region_typed<float, true>(p, stream)
-                           : launch_region_typed<float, false>(p, stream);
+            return softmax ? launch_region_typed<float, true>(p, windows, stream)
+                           : launch_region_typed<float, false>(p, windows, stream);
         case 1:
-            return softmax ? launch_region_typed<__half, true>(p, stream)
-                           : launch_region_typed<__half, false>(p, stream);
+            return softmax ? launch_region_typed<__half, true>(p, windows, stream)
+                           : launch_region_typed<__half, false>(p, windows, stream);
         case 2:
-            return softmax ? launch_region_typed<__nv_bfloat16, true>(p, stream)
-                           : launch_region_typed<__nv_bfloat16, false>(p, stream);
+            return softmax ? launch_region_typed<__nv_bfloat16, true>(p, windows, stream)
+                           : launch_region_typed<__nv_bfloat16, false>(p, windows, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -54,6 +54,7 @@ struct Params {
     int point_chunk;        // descriptors per pair held in shared memory at a time
     int64_t num_groups;     // ceil(B*Q*G / pairs per warp)
     unsigned grid;
+    int region_window_ints; // region-tiled backward: int32 window accumulators per CTA (0: none)
 };
 
 // ---------------------------------------------------------------------------------
@@ -369,7 +370,8 @@ size_t forward_smem_bytes(const Params &p, bool softmax);
 size_t backward_smem_bytes(const Params &p, bool softmax);
 // region-tiled backward for encoder calls (msda_backward_region.cu)
 bool backward_region_eligible(const Params &p, int dtype, bool softmax);
-cudaError_t launch_backward_region(const Params &p, int dtype, bool softmax, cudaStream_t stream);
+cudaError_t launch_backward_region(const Params &p, int dtype, bool softmax, bool windows,
+                                   cudaStream_t stream);
 
 // L2 access-policy window over the value tensor (msda_l2_window.cu): fills `attr` and returns
 // 1 when the opt-in feature is on, else 0
