@@ -28,15 +28,26 @@
 // prepare_kernel clears exactly what the backward kernel adds into.
 #include "msda_common.cuh"
 
+// tuning knobs (compile-time): points in flight together and CTAs per SM the registers allow.
+// Measured on B200 at the headline shape (backward call, ms): unroll 1 / 4 CTAs 0.611,
+// 1 / 3 0.618, 2 / 3 0.633, 3 / 3 0.648, 2 / 4 0.688, 2 / 2 0.734, 1 / 5 0.833.
+#ifndef MSDA_BWD_UNROLL
+#define MSDA_BWD_UNROLL 1
+#endif
+#ifndef MSDA_BWD_MIN_CTAS
+#define MSDA_BWD_MIN_CTAS 4
+#endif
+
 namespace msda_b200 {
 
 namespace {
 
 template <typename T, bool SOFTMAX>
-__global__ void __launch_bounds__(256, 3) backward_kernel(const Params p) {
+__global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const Params p) {
     using VT = VecTraits<T>;
     constexpr int V = VT::kVec;
     constexpr int NV2 = V / 2;
+    constexpr int kUnroll = MSDA_BWD_UNROLL;
     extern __shared__ uint4 smem[];
     __shared__ LevelTable lt;
 
@@ -146,7 +157,7 @@ __global__ void __launch_bounds__(256, 3) backward_kernel(const Params p) {
                 const T *vc = value + sample + ch;
                 T *gc = grad_value + sample + ch;
                 T *sc = scratch + scratch_sample + ch;
-#pragma unroll 2
+#pragma unroll kUnroll
                 for (int j = 0; j < pc; ++j) {
                     const uint4 A = dp[2 * j];
                     const uint4 Fr = dp[2 * j + 1];
