@@ -248,10 +248,17 @@ class _MSDA:
         reason = unsupported_reason(context)
         if reason is not None:
             raise NoBackendError(f"msda cannot run this call: {reason}")
+        use_softmax = context.method is Method.SOFTMAX
+        if backend is None and not (set(options) - {"chunk_step"}):
+            # like the reference's backend=None route (registry/msda.py:415-452): go through the
+            # public operator, so that Dynamo and torch.export record `deformops_b200::msda`
+            op = (torch.ops.deformops_b200.msda_softmax if use_softmax
+                  else torch.ops.deformops_b200.msda)
+            return op(value, spatial_shapes, level_start_index, sampling_locations,
+                      attention_weights)
         return forward(value, spatial_shapes, level_start_index, sampling_locations,
                        attention_weights, options.get("chunk_step", 128),
-                       num_points=options.get("num_points"),
-                       softmax=context.method is Method.SOFTMAX)
+                       num_points=options.get("num_points"), softmax=use_softmax)
 
 
 msda = _MSDA()

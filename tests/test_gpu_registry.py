@@ -178,3 +178,37 @@ def test_autocast_keeps_float32_locations():
     e = orc.forward(t["value"].cpu(), c["spatial_shapes"], c["level_start_index"], t["loc"].cpu(),
                     t["attn_linear"].cpu())
     assert rel_err(to_np(out), e) < 1e-2
+
+
+def test_export_and_dynamo_record_the_public_op():
+    """torch.export keeps the public op in the graph and decomposes it to the private forward op;
+    Dynamo traces the functional without a graph break (dynamic query count included)."""
+    from deformops_b200.registry import msda
+
+    _, t = _case("small_b")
+    args = (t["value"], t["shapes"], t["starts"], t["loc"], t["attn_linear"])
+
+    class Layer(torch.nn.Module):
+        def forward(self, value, shapes, starts, loc, attn):
+            return msda(value, shapes, starts, loc, attn, method="softmax")
+
+    exported = torch.export.export(Layer(), args)
+    targets = [str(n.target) for n in exported.graph.nodes if n.op == "call_function"]
+    assert any("deformops_b200.msda_softmax" in x for x in targets), targets
+    decomposed = exported.run_decompositions()
+    targets = [str(n.target) for n in decomposed.graph.nodes if n.op == "call_function"]
+    assert any("deformops_b200.msda_softmax_forward" in x for x in targets), targets
+    assert torch.equal(decomposed.module()(*args), Layer()(*args))
+
+    seen = []
+
+    def backend(gm, example_inputs):
+        seen.extend(str(n.target) for n in gm.graph.nodes if n.op == "call_function")
+        return gm.forward
+
+    compiled = torch.compile(Layer(), backend=backend, fullgraph=True, dynamic=True)
+    out = compiled(*args)
+    assert torch.equal(out, Layer()(*args))
+    assert any("deformops_b200.msda_softmax" in x for x in seen), seen
+    fewer = (t["value"], t["shapes"], t["starts"], t["loc"][:, :5], t["attn_linear"][:, :5])
+    assert torch.equal(compiled(*fewer), Layer()(*fewer))
