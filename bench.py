@@ -62,7 +62,7 @@ def parse():
     ap.add_argument("--e2e-sequential", action="store_true",
                     help="e2e leg without overlap: upload, compute, download one after another")
     ap.add_argument("--no-scratch", action="store_true",
-                    help="backward without the float32 accumulator (direct 16-bit reductions)")
+                    help="backward without the replica scratch (every level adds straight into grad_value)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0,
                     help="target CPU time of the cpu_baseline sample")
@@ -265,7 +265,7 @@ def main():
     stream = torch.cuda.current_stream()
     sptr = ctypes.c_void_p(stream.cuda_stream)
 
-    # float32 accumulator the backward uses for the coarse levels of a 16-bit grad_value
+    # scratch for the replica accumulators of a 16-bit grad_value (see msda_b200_backward)
     nscratch = 0 if args.no_scratch else shim.scratch_bytes(Bq, S, G, D, code)
     scratch = torch.empty(max(nscratch // 4, 1), dtype=torch.float32, device=device)
     scr = _p(scratch) if nscratch else None

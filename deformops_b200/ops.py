@@ -152,7 +152,7 @@ def _make_backward(softmax: bool) -> Callable[..., tuple[Tensor, Tensor, Tensor]
         shim = load_library()
         value, loc, attn, grad_output = map(_aligned, (value, loc, attn, grad_output))
         stream = torch.cuda.current_stream(value.device).cuda_stream
-        # float32 accumulator for the coarse levels of a 16-bit grad_value; comes from torch's
+        # scratch for the replica accumulators of a 16-bit grad_value; comes from torch's
         # caching allocator, only the rows of the levels that use it are ever touched
         nbytes = shim.scratch_bytes(B, S, G, D, DTYPE_CODES[value.dtype]) if Q > 0 else 0
         scratch = (torch.empty(nbytes // 4, dtype=torch.float32, device=value.device)

@@ -42,7 +42,7 @@ def abi_forward(value, shapes, starts, loc, attn, *, softmax=False, stream=None)
 
 def abi_backward(value, shapes, starts, loc, attn, grad_out, *, softmax=False, zero=True,
                  scratch=True, scratch_adds=0):
-    """``scratch=True`` hands the call the float32 accumulator the product path uses for
+    """``scratch=True`` hands the call the replica scratch the product path uses for
     16-bit dtypes; ``scratch=False`` forces direct 16-bit reductions on every level."""
     shim = load_library()
     B, S, G, D, Q, L, K = dims(value, loc)
