@@ -180,6 +180,41 @@ def test_autocast_keeps_float32_locations():
     assert rel_err(to_np(out), e) < 1e-2
 
 
+def test_forward_and_backward_replay_from_a_cuda_graph():
+    """The call path never synchronises with the host and reads the level table on the device,
+    so forward + backward can be captured once and replayed on new data."""
+    from deformops_b200.registry import msda
+
+    _, t = _case("small_b", torch.bfloat16)
+    value = t["value"].clone().requires_grad_(True)
+    loc = t["loc"].clone().requires_grad_(True)
+    attn = t["attn_linear"].clone().requires_grad_(True)
+
+    def step():
+        out = msda(value, t["shapes"], t["starts"], loc, attn)
+        grads = torch.autograd.grad(out, [value, loc, attn], t["grad_out"])
+        return out, grads
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):          # warm-up outside capture: library load, allocator
+        for _ in range(2):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out, grads = step()
+    with torch.no_grad():                   # new inputs in the captured buffers
+        value.mul_(0.5)
+        loc.add_(0.01)
+    graph.replay()
+    torch.cuda.synchronize()
+    e_out, e_grads = step()
+    assert torch.equal(out, e_out)
+    assert torch.equal(grads[1], e_grads[1]) and torch.equal(grads[2], e_grads[2])
+    torch.testing.assert_close(grads[0], e_grads[0], rtol=2e-2, atol=2e-2)
+
+
 def test_export_and_dynamo_record_the_public_op():
     """torch.export keeps the public op in the graph and decomposes it to the private forward op;
     Dynamo traces the functional without a graph break (dynamic query count included)."""
