@@ -8,4 +8,4 @@ __version__ = "0.1.0"
 
 from .core.errors import KernelBuildError, KernelUnavailableError, NoBackendError  # noqa: F401
 from .core.runtime import Method  # noqa: F401
-from .registry import Backend, MSDABackend, MSDAContext, msda  # noqa: F401
+from .registry import Backend, MSDABackend, MSDAContext, msda, msda_from_offsets  # noqa: F401

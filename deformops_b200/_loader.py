@@ -19,7 +19,7 @@ from .core.errors import KernelBuildError, KernelUnavailableError
 
 __all__ = ["ABI_VERSION", "Shim", "library_path", "load_library", "loaded"]
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 _lock = threading.Lock()
 _shim: "Shim | None" = None
@@ -41,6 +41,7 @@ class Shim:
     #: every symbol ``include/msda_b200.h`` declares
     SYMBOLS = ("msda_b200_abi_version", "msda_b200_last_error", "msda_b200_forward",
                "msda_b200_backward", "msda_b200_backward_scratch_bytes",
+               "msda_b200_forward_offsets", "msda_b200_backward_offsets",
                "msda_b200_backward_static_scratch", "msda_b200_launch_geometry")
 
     def __init__(self, path: str):
@@ -63,6 +64,15 @@ class Shim:
         self.scratch_bytes = self.lib.msda_b200_backward_scratch_bytes
         self.scratch_bytes.restype = _i64
         self.scratch_bytes.argtypes = [_i64] * 4 + [_int]
+        self.forward_offsets = self.lib.msda_b200_forward_offsets
+        self.forward_offsets.restype = _int
+        self.forward_offsets.argtypes = ([_vp] * 4 + [_int, _vp, _int, _vp, _vp] + [_i64] * 7
+                                         + [_int, _int, _int, _vp])
+        self.backward_offsets = self.lib.msda_b200_backward_offsets
+        self.backward_offsets.restype = _int
+        self.backward_offsets.argtypes = ([_vp] * 4 + [_int, _vp, _int] + [_vp] * 6
+                                          + [_i64, _i64] + [_i64] * 7
+                                          + [_int, _int, _int, _int, _vp])
         self.backward_static_scratch = self.lib.msda_b200_backward_static_scratch
         self.backward_static_scratch.restype = _int
         self.backward_static_scratch.argtypes = ([_vp] * 9 + [_i64] + [_i64] * 7

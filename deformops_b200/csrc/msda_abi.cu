@@ -109,6 +109,39 @@ int cuda_fail(cudaError_t e, const char *what) {
                 cudaGetErrorString(e));
 }
 
+// Where the sample locations come from: a location tensor, or predicted offsets plus
+// reference points (the kernels then do the layer's location arithmetic themselves).
+struct Points {
+    const void *data;        // locations (float32) or offsets
+    void *grad;              // gradient of `data`, same layout and element type (backward)
+    const float *ref;        // reference points, or null when `data` holds locations
+    int ref_coords;
+    int offsets16;
+};
+
+int check_points(const Points &pts, int offsets_dtype, int dtype, const char *who) {
+    if (pts.ref_coords != 2 && pts.ref_coords != 4)
+        return fail(MSDA_B200_INVALID_ARGUMENT,
+                    "%s: reference points carry %d coordinates; 2 (x, y) or 4 (cx, cy, w, h) "
+                    "are supported", who, pts.ref_coords);
+    if (offsets_dtype != MSDA_B200_F32 && offsets_dtype != dtype)
+        return fail(MSDA_B200_INVALID_ARGUMENT,
+                    "%s: offsets must be float32 or the value dtype (got %d for value dtype %d)",
+                    who, offsets_dtype, dtype);
+    return MSDA_B200_OK;
+}
+
+int forward_impl(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
+                 const Points &pts, const void *attn, void *out, int64_t B, int64_t S, int64_t G,
+                 int64_t D, int64_t Q, int64_t L, int64_t K, int dtype, int apply_softmax,
+                 int device, void *stream);
+int backward_impl(const void *value, const int64_t *spatial_shapes,
+                  const int64_t *level_start_index, const Points &pts, const void *attn,
+                  const void *grad_out, void *grad_value, void *grad_attn, void *scratch,
+                  int64_t scratch_bytes, int64_t scratch_adds, int64_t B, int64_t S, int64_t G,
+                  int64_t D, int64_t Q, int64_t L, int64_t K, int dtype, int apply_softmax,
+                  int zero_grad_value, int device, void *stream);
+
 }  // namespace
 
 namespace msda_b200 {
@@ -144,6 +177,69 @@ int msda_b200_forward(const void *value, const int64_t *spatial_shapes,
                       const int64_t *level_start_index, const float *loc, const void *attn,
                       void *out, int64_t B, int64_t S, int64_t G, int64_t D, int64_t Q, int64_t L,
                       int64_t K, int dtype, int apply_softmax, int device, void *stream) {
+    const Points pts{loc, nullptr, nullptr, 0, 0};
+    return forward_impl(value, spatial_shapes, level_start_index, pts, attn, out, B, S, G, D, Q, L,
+                        K, dtype, apply_softmax, device, stream);
+}
+
+int msda_b200_forward_offsets(const void *value, const int64_t *spatial_shapes,
+                              const int64_t *level_start_index, const float *reference_points,
+                              int ref_coords, const void *offsets, int offsets_dtype,
+                              const void *attn, void *out, int64_t B, int64_t S, int64_t G,
+                              int64_t D, int64_t Q, int64_t L, int64_t K, int dtype,
+                              int apply_softmax, int device, void *stream) {
+    const Points pts{offsets, nullptr, reference_points, ref_coords,
+                     offsets_dtype != MSDA_B200_F32};
+    const int st = check_points(pts, offsets_dtype, dtype, "forward_offsets");
+    if (st != MSDA_B200_OK) return st;
+    if (B > 0 && Q > 0 && (!reference_points || !aligned16(reference_points)))
+        return fail(MSDA_B200_INVALID_ARGUMENT,
+                    "forward_offsets: reference_points is null or not 16-byte aligned");
+    return forward_impl(value, spatial_shapes, level_start_index, pts, attn, out, B, S, G, D, Q, L,
+                        K, dtype, apply_softmax, device, stream);
+}
+
+int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
+                       const int64_t *level_start_index, const float *loc, const void *attn,
+                       const void *grad_out, void *grad_value, float *grad_loc, void *grad_attn,
+                       void *scratch, int64_t scratch_bytes, int64_t scratch_adds, int64_t B,
+                       int64_t S, int64_t G, int64_t D, int64_t Q, int64_t L, int64_t K, int dtype,
+                       int apply_softmax, int zero_grad_value, int device, void *stream) {
+    const Points pts{loc, grad_loc, nullptr, 0, 0};
+    return backward_impl(value, spatial_shapes, level_start_index, pts, attn, grad_out, grad_value,
+                         grad_attn, scratch, scratch_bytes, scratch_adds, B, S, G, D, Q, L, K,
+                         dtype, apply_softmax, zero_grad_value, device, stream);
+}
+
+int msda_b200_backward_offsets(const void *value, const int64_t *spatial_shapes,
+                               const int64_t *level_start_index, const float *reference_points,
+                               int ref_coords, const void *offsets, int offsets_dtype,
+                               const void *attn, const void *grad_out, void *grad_value,
+                               void *grad_offsets, void *grad_attn, void *scratch,
+                               int64_t scratch_bytes, int64_t scratch_adds, int64_t B, int64_t S,
+                               int64_t G, int64_t D, int64_t Q, int64_t L, int64_t K, int dtype,
+                               int apply_softmax, int zero_grad_value, int device, void *stream) {
+    const Points pts{offsets, grad_offsets, reference_points, ref_coords,
+                     offsets_dtype != MSDA_B200_F32};
+    const int st = check_points(pts, offsets_dtype, dtype, "backward_offsets");
+    if (st != MSDA_B200_OK) return st;
+    if (B > 0 && Q > 0 && (!reference_points || !aligned16(reference_points)))
+        return fail(MSDA_B200_INVALID_ARGUMENT,
+                    "backward_offsets: reference_points is null or not 16-byte aligned");
+    return backward_impl(value, spatial_shapes, level_start_index, pts, attn, grad_out, grad_value,
+                         grad_attn, scratch, scratch_bytes, scratch_adds, B, S, G, D, Q, L, K,
+                         dtype, apply_softmax, zero_grad_value, device, stream);
+}
+
+}  // extern "C"
+
+namespace {
+
+int forward_impl(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
+                 const Points &pts, const void *attn, void *out, int64_t B, int64_t S, int64_t G,
+                 int64_t D, int64_t Q, int64_t L, int64_t K, int dtype, int apply_softmax,
+                 int device, void *stream) {
+    const void *loc = pts.data;
     msda_b200::Params p{};
     const int st = plan(p, B, S, G, D, Q, L, K, dtype, apply_softmax != 0);
     if (st != MSDA_B200_OK) return st;
@@ -156,7 +252,10 @@ int msda_b200_forward(const void *value, const int64_t *spatial_shapes,
     p.value = value;
     p.spatial_shapes = spatial_shapes;
     p.level_start_index = level_start_index;
-    p.loc = loc;
+    p.loc = static_cast<const float *>(loc);
+    p.ref = pts.ref;
+    p.ref_coords = pts.ref_coords;
+    p.offsets16 = pts.offsets16;
     p.attn = attn;
     p.out = out;
     DeviceGuard guard(device);
@@ -167,12 +266,14 @@ int msda_b200_forward(const void *value, const int64_t *spatial_shapes,
     return MSDA_B200_OK;
 }
 
-int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
-                       const int64_t *level_start_index, const float *loc, const void *attn,
-                       const void *grad_out, void *grad_value, float *grad_loc, void *grad_attn,
-                       void *scratch, int64_t scratch_bytes, int64_t scratch_adds, int64_t B,
-                       int64_t S, int64_t G, int64_t D, int64_t Q, int64_t L, int64_t K, int dtype,
-                       int apply_softmax, int zero_grad_value, int device, void *stream) {
+int backward_impl(const void *value, const int64_t *spatial_shapes,
+                  const int64_t *level_start_index, const Points &pts, const void *attn,
+                  const void *grad_out, void *grad_value, void *grad_attn, void *scratch,
+                  int64_t scratch_bytes, int64_t scratch_adds, int64_t B, int64_t S, int64_t G,
+                  int64_t D, int64_t Q, int64_t L, int64_t K, int dtype, int apply_softmax,
+                  int zero_grad_value, int device, void *stream) {
+    const void *loc = pts.data;
+    void *grad_loc = pts.grad;
     msda_b200::Params p{};
     const int st = plan(p, B, S, G, D, Q, L, K, dtype, apply_softmax != 0);
     if (st != MSDA_B200_OK) return st;
@@ -207,11 +308,14 @@ int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
     p.value = value;
     p.spatial_shapes = spatial_shapes;
     p.level_start_index = level_start_index;
-    p.loc = loc;
+    p.loc = static_cast<const float *>(loc);
+    p.ref = pts.ref;
+    p.ref_coords = pts.ref_coords;
+    p.offsets16 = pts.offsets16;
     p.attn = attn;
     p.grad_out = grad_out;
     p.grad_value = grad_value;
-    p.grad_loc = grad_loc;
+    p.grad_loc = static_cast<float *>(grad_loc);
     p.grad_attn = grad_attn;
     p.scratch = use_scratch ? static_cast<float *>(scratch) : nullptr;
     p.scratch_adds = scratch_adds > 0 ? scratch_adds : (dtype == MSDA_B200_BF16 ? 12 : 256);
@@ -247,4 +351,4 @@ int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
     return MSDA_B200_OK;
 }
 
-}  // extern "C"
+}  // namespace

@@ -84,7 +84,6 @@ __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const 
     const T *value = reinterpret_cast<const T *>(p.value);
     const T *attn = reinterpret_cast<const T *>(p.attn);
     const T *grad_out = reinterpret_cast<const T *>(p.grad_out);
-    const float2 *loc2 = reinterpret_cast<const float2 *>(p.loc);
     T *grad_value = reinterpret_cast<T *>(p.grad_value);
     T *scratch = reinterpret_cast<T *>(p.scratch);
 
@@ -115,14 +114,16 @@ __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const 
                 uint4 A = make_uint4(0u, 0u, 0u, 0u), Fr = make_uint4(0u, 0u, 0u, 0u);
                 if (sl < nlive) {
                     const int64_t e = (pair0 + sl) * P + pt;
-                    const float2 xy = ld_stream_f2(loc2 + e);
+                    const int l = (int)(((float)pt + 0.5f) * inv_K);  // pt / K
+                    float2 dpix;
+                    const float2 xy = sample_location<T>(p, e, pair0 + sl, l, (float)lt.W[l],
+                                                         (float)lt.H[l], dpix);
                     float a = VT::to_float(attn[e]);
                     if constexpr (SOFTMAX) {
                         const float2 st = s_stats[sl];
                         a = expf(a - st.x) * st.y;
                         s_prob[sl * P + pt] = a;
                     }
-                    const int l = (int)(((float)pt + 0.5f) * inv_K);  // pt / K
                     const PointGeom geo = locate(xy.x, xy.y, lt.H[l], lt.W[l], lt.start[l], GD);
                     // a skipped point contributes exact zeros whatever its weight holds
                     const float au = (geo.flags & kInside) ? a : 0.f;
@@ -137,7 +138,7 @@ __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const 
                     }
                     A = make_uint4((unsigned)geo.off00, red_off, flags, __float_as_uint(au));
                     Fr = make_uint4(__float_as_uint(geo.fr), __float_as_uint(geo.fc),
-                                    __float_as_uint(au * geo.Wf), __float_as_uint(au * geo.Hf));
+                                    __float_as_uint(au * dpix.x), __float_as_uint(au * dpix.y));
                 }
                 desc[sl * DS + 2 * j] = A;
                 desc[sl * DS + 2 * j + 1] = Fr;
@@ -240,7 +241,15 @@ __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const 
                 const int sl = (int)(((float)idx + 0.5f) * inv_P);
                 ga = s_prob[idx] * (ga - s_stats[sl].x);
             }
-            st_stream_f2(gl_out + idx, s_gloc[idx]);
+            if constexpr (sizeof(T) == 2) {
+                // offsets predicted in the value dtype get their gradient in that dtype
+                if (p.ref != nullptr && p.offsets16)
+                    reinterpret_cast<uint32_t *>(p.grad_loc)[pair0 * P + idx] = VT::pack2(s_gloc[idx]);
+                else
+                    st_stream_f2(gl_out + idx, s_gloc[idx]);
+            } else {
+                st_stream_f2(gl_out + idx, s_gloc[idx]);
+            }
             ga_out[idx] = VT::from_float(ga);
         }
         __syncwarp();

@@ -528,6 +528,7 @@ size_t backward_region_smem_bytes(const Params &p, bool softmax, int threads, in
 bool backward_region_eligible(const Params &p, int dtype, bool softmax) {
     const int vec = dtype == 0 ? 4 : 8;
     const int ppw = 32 >> p.lph_log2;
+    if (p.ref != nullptr) return false;                     // reads locations, not offsets
     if (p.Q != p.S || p.Q >= (1ll << 31) || p.D > 32 * vec || p.D % vec != 0) return false;
     if ((1 << p.lph_log2) * vec != p.D) return false;      // every lane of a slot carries channels
     if (ppw * p.K > 128 || p.D * 4 > kWindowInts) return false;

@@ -55,6 +55,13 @@ struct Params {
     int64_t num_groups;     // ceil(B*Q*G / pairs per warp)
     unsigned grid;
     int region_window_ints; // region-tiled backward: int32 window accumulators per CTA (0: none)
+    // Fused location arithmetic.  When `ref` is set, `loc` / `grad_loc` hold the predicted
+    // offsets (B,Q,G,L,K,2) and their gradient, and a point samples at
+    //   ref_coords == 2:  ref.xy + offset / (W_l, H_l)
+    //   ref_coords == 4:  ref.xy + offset / K * ref.wh * 0.5      (ref = cx, cy, w, h)
+    const float *ref;       // (B,Q,L,ref_coords) float32, or null: `loc` holds locations
+    int ref_coords;
+    int offsets16;          // offsets and their gradient are stored in the 16-bit value dtype
 };
 
 // ---------------------------------------------------------------------------------
@@ -92,6 +99,9 @@ template <> struct VecTraits<__nv_bfloat16> {
         for (int i = 0; i < 4; ++i)
             f[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
     }
+    __device__ static __forceinline__ float2 unpack2(uint32_t w) {
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    }
     __device__ static __forceinline__ uint32_t pack2(float2 v) {
         uint32_t r;  // cvt packs {upper, lower} with round-to-nearest-even
         asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(v.y), "f"(v.x));
@@ -119,6 +129,9 @@ template <> struct VecTraits<__half> {
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) f[i] = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+    }
+    __device__ static __forceinline__ float2 unpack2(uint32_t w) {
+        return __half22float2(*reinterpret_cast<const __half2 *>(&w));
     }
     __device__ static __forceinline__ uint32_t pack2(float2 v) {
         const __half2 h = __float22half2_rn(v);
@@ -341,6 +354,41 @@ __device__ __forceinline__ PointGeom locate(float x, float y, int H, int W, int 
     g.off00 = (start + r0 * W + c0) * GD;
     g.rowstride = W * GD;
     return g;
+}
+
+// Sample location of element `e` = (pair, point) of level `l`, and in `dpix` the derivative of
+// the pixel coordinate with respect to what the caller differentiates: the location itself
+// (W, H), or the predicted offset when the call carries reference points.  The offset
+// arithmetic follows the torch expressions of the layers it replaces, in float32:
+// `ref + offset / (W, H)` and `ref.xy + offset / K * ref.wh * 0.5`.
+template <typename T>
+__device__ __forceinline__ float2 sample_location(const Params &p, int64_t e, int64_t pair, int l,
+                                                  float Wf, float Hf, float2 &dpix) {
+    const float2 *loc2 = reinterpret_cast<const float2 *>(p.loc);
+    if (p.ref == nullptr) {
+        dpix = make_float2(Wf, Hf);
+        return ld_stream_f2(loc2 + e);
+    }
+    float2 off;
+    if constexpr (sizeof(T) == 2) {
+        if (p.offsets16)
+            off = VecTraits<T>::unpack2(__ldg(reinterpret_cast<const uint32_t *>(p.loc) + e));
+        else
+            off = ld_stream_f2(loc2 + e);
+    } else {
+        off = ld_stream_f2(loc2 + e);
+    }
+    const int64_t bq = pair / p.G;
+    if (p.ref_coords == 2) {
+        const float2 r = __ldg(reinterpret_cast<const float2 *>(p.ref) + bq * p.L + l);
+        dpix = make_float2(1.f, 1.f);
+        return make_float2(r.x + off.x / Wf, r.y + off.y / Hf);
+    }
+    const float4 r = __ldg(reinterpret_cast<const float4 *>(p.ref) + bq * p.L + l);
+    const float Kf = (float)p.K;
+    // d(location)/d(offset) = wh * 0.5 / K, evaluated as the forward expression at offset 1
+    dpix = make_float2(Wf * (1.f / Kf * r.z * 0.5f), Hf * (1.f / Kf * r.w * 0.5f));
+    return make_float2(r.x + off.x / Kf * r.z * 0.5f, r.y + off.y / Kf * r.w * 0.5f);
 }
 
 // softmax statistics of one pair's P logits: (max, 1 / sum of exp(logit - max))

@@ -63,7 +63,6 @@ __global__ void __launch_bounds__(256, MSDA_FWD_MIN_CTAS) forward_kernel(const P
     const int sub = lane & (lph - 1);
     const T *value = reinterpret_cast<const T *>(p.value);
     const T *attn = reinterpret_cast<const T *>(p.attn);
-    const float2 *loc2 = reinterpret_cast<const float2 *>(p.loc);
     T *out = reinterpret_cast<T *>(p.out);
 
     for (int64_t group = (int64_t)blockIdx.x * nwarps + warp; group < p.num_groups;
@@ -93,13 +92,15 @@ __global__ void __launch_bounds__(256, MSDA_FWD_MIN_CTAS) forward_kernel(const P
                 uint4 A = make_uint4(0u, 0u, 0u, 0u), Wt = make_uint4(0u, 0u, 0u, 0u);
                 if (sl < nlive) {
                     const int64_t e = (pair0 + sl) * P + pt;
-                    const float2 xy = ld_stream_f2(loc2 + e);
+                    const int l = (int)(((float)pt + 0.5f) * inv_K);  // pt / K
+                    float2 dpix;
+                    const float2 xy = sample_location<T>(p, e, pair0 + sl, l, (float)lt.W[l],
+                                                         (float)lt.H[l], dpix);
                     float a = VT::to_float(attn[e]);
                     if constexpr (SOFTMAX) {
                         const float2 st = stats[sl];
                         a = expf(a - st.x) * st.y;
                     }
-                    const int l = (int)(((float)pt + 0.5f) * inv_K);  // pt / K
                     const PointGeom geo = locate(xy.x, xy.y, lt.H[l], lt.W[l], lt.start[l], GD);
                     // A corner outside the level keeps weight 0 and is pointed at the nearest
                     // pixel inside it, so the gather needs no predicates; a skipped point

@@ -13,6 +13,9 @@ Drop-in subclasses of the two Hugging Face classes the reference replaces
   raw logits go to the SOFTMAX operator, which normalises inside the kernel, so one
   elementwise pass over the weights disappears from forward and backward.  The normalised
   weights are only materialised when the caller asks for them (``output_attentions``).
+  The location arithmetic (``reference_points + offsets / (W, H)``, ``transformers.py:195-218``)
+  is fused the same way: offsets and reference points go to the kernel as they are and no
+  location tensor is written or read back.
 
 Parameters keep their Hugging Face names, so pretrained checkpoints load unchanged.
 """
@@ -25,7 +28,8 @@ import torch
 from torch import Tensor, nn
 
 from ..core.runtime import Method
-from ..registry.msda import Backend, MSDABackend
+from ..registry.msda import (Backend, MSDABackend, locations_from_offsets, msda,
+                             msda_from_offsets)
 from ._ops import run_msda
 
 try:
@@ -91,18 +95,22 @@ class Mask2FormerPixelDecoderEncoderMultiscaleDeformableAttention(_HF_M2F):
         offsets = self.sampling_offsets(hidden_states).view(B, Q, G, L, K, 2)
         logits = self.attention_weights(hidden_states).view(B, Q, G, L * K)
 
-        ref = reference_points[:, :, None, :, None, :]
-        if reference_points.shape[-1] == 2:
-            normalizer = shapes.flip(-1).to(offsets.dtype)       # (L, 2) as (width, height)
-            locations = ref + offsets / normalizer[None, None, None, :, None, :]
-        elif reference_points.shape[-1] == 4:
-            locations = ref[..., :2] + offsets / K * ref[..., 2:] * 0.5
-        else:
+        if reference_points.shape[-1] not in (2, 4):
             raise ValueError("Last dim of reference_points must be 2 or 4, but got "
                              f"{reference_points.shape[-1]}")
-
-        out = run_msda(value, shapes, level_start_index, locations, logits,
-                       chunk_step=self.im2col_step, backend=self.backend, method=Method.SOFTMAX)
+        if isinstance(self.backend, MSDABackend):
+            locations = locations_from_offsets(reference_points, offsets, shapes)
+            out = run_msda(value, shapes, level_start_index, locations, logits,
+                           chunk_step=self.im2col_step, backend=self.backend,
+                           method=Method.SOFTMAX)
+        else:
+            # softmax and `reference + offsets / (W, H)` both happen inside the kernel
+            msda._only_cuda(self.backend)
+            if level_start_index is None:
+                sizes = shapes[:, 0] * shapes[:, 1]
+                level_start_index = torch.cumsum(sizes, 0) - sizes
+            out = msda_from_offsets(value, shapes, level_start_index, reference_points, offsets,
+                                    logits, method=Method.SOFTMAX)
         weights = torch.softmax(logits, -1).view(B, Q, G, L, K) if output_attentions else None
         return self.output_proj(out), weights
 

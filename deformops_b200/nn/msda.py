@@ -13,8 +13,9 @@ the other and a model can swap the class without further edits:
 * ``load_state_dict`` renames Deformable-DETR keys (``sampling_offsets``,
   ``attention_weights``, ``value_proj``, ``output_proj``) for metadata versions below 2.
 
-The sampling itself is one call of :data:`deformops_b200.registry.msda` (default
-``method="softmax"``: the logits are normalised inside the kernel).
+The sampling itself is one call of :func:`deformops_b200.registry.msda_from_offsets` (default
+``method="softmax"``: the logits are normalised and the offsets added to the reference points
+inside the kernel; neither normalised weights nor a location tensor are materialised).
 """
 
 from __future__ import annotations
@@ -26,7 +27,7 @@ import torch
 from torch import Tensor, nn
 
 from ..core.runtime import Method
-from ..registry.msda import Backend, MSDABackend, msda
+from ..registry.msda import Backend, MSDABackend, msda, msda_from_offsets
 
 __all__ = ["MultiScaleDeformAttn2d"]
 
@@ -62,6 +63,8 @@ class MultiScaleDeformAttn2d(nn.Module):
         self.method = Method(method)
         self.backend = backend
         self.chunk_step = chunk_step
+        #: let the kernels do the location arithmetic (set False to build locations in torch)
+        self.fuse_locations = True
 
         samples = num_heads * num_levels * num_points
         self.proj_offset = nn.Linear(dim, samples * 2)
@@ -125,12 +128,21 @@ class MultiScaleDeformAttn2d(nn.Module):
         value = value.view(B, N, self.num_heads, self.dim // self.num_heads)
         weights = self.proj_weights(q).view(B, Q, self.num_heads,
                                             self.num_levels * self.num_points)
-        locations = self.sampling_locations(q, p, spatial_shapes)
 
         if isinstance(self.backend, MSDABackend):
+            locations = self.sampling_locations(q, p, spatial_shapes)
             out = self.backend.forward(value, spatial_shapes, level_start_index, locations,
                                        weights, self.chunk_step, self.method)
+        elif self.fuse_locations:
+            # the kernels add the offsets to the reference points themselves; no location
+            # tensor is built
+            msda._only_cuda(self.backend)
+            offset = self.proj_offset(q).view(B, Q, self.num_heads, self.num_levels,
+                                              self.num_points, 2)
+            out = msda_from_offsets(value, spatial_shapes, level_start_index, p, offset, weights,
+                                    method=self.method)
         else:
+            locations = self.sampling_locations(q, p, spatial_shapes)
             options: dict[str, Any] = {"method": self.method, "backend": self.backend}
             if self.backend is not None:
                 options["chunk_step"] = self.chunk_step

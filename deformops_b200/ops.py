@@ -17,6 +17,9 @@ pointers plus the current stream to ``libmsda_b200.so``; there is no other imple
 (a CPU tensor reaching these ops is an error).  Meta kernels and the autograd formula
 follow ``sources/deformops/backends/cuda/_msda_bridge.py:146-299``.
 
+``msda_offsets_forward`` / ``msda_offsets_backward`` have no counterpart in the reference: they
+take reference points and predicted offsets instead of locations (see further down).
+
 Public ops ``deformops_b200::msda`` and ``deformops_b200::msda_softmax`` take the five
 tensors only (``sources/deformops/registry/msda.py:366-412``); they are
 CompositeImplicitAutograd over the private ops and carry a vmap rule that folds the
@@ -35,7 +38,8 @@ from torch.autograd.function import once_differentiable
 
 from ._loader import load_library
 
-__all__ = ["NAMESPACE", "PRIVATE_OPS", "PUBLIC_OPS", "DTYPE_CODES", "launch_counter"]
+__all__ = ["NAMESPACE", "OFFSETS_OPS", "PRIVATE_OPS", "PUBLIC_OPS", "DTYPE_CODES",
+           "launch_counter"]
 
 NAMESPACE = "deformops_b200"
 
@@ -229,6 +233,162 @@ def _define_private_ops() -> None:
             setup_context=_setup_context)
 
 
+# --- ops with the layer's location arithmetic fused in -----------------------------------------
+# No counterpart among the reference's operators: its layers compute
+# ``reference_points + offsets / (W, H)`` (or the box form) in torch and hand the op a
+# location tensor (``sources/deformops/nn/msda.py:222-239``).  These ops take the reference
+# points and the predicted offsets instead; the kernels form each location in registers.
+_OFFSETS_FORWARD_SCHEMA = (
+    "(Tensor value, Tensor spatial_shapes, Tensor level_start_index, Tensor reference_points, "
+    "Tensor offsets, Tensor attn, bool softmax) -> Tensor"
+)
+_OFFSETS_BACKWARD_SCHEMA = (
+    "(Tensor value, Tensor spatial_shapes, Tensor level_start_index, Tensor reference_points, "
+    "Tensor offsets, Tensor attn, Tensor grad_output, bool softmax) -> (Tensor, Tensor, Tensor)"
+)
+OFFSETS_OPS = ("msda_offsets_forward", "msda_offsets_backward")
+
+
+def _check_offsets_operands(value: Tensor, shapes: Tensor, starts: Tensor, ref: Tensor,
+                            offsets: Tensor, attn: Tensor):
+    if offsets.dtype != torch.float32 and offsets.dtype != value.dtype:
+        raise RuntimeError(f"offsets must be float32 or the value dtype {value.dtype}, "
+                           f"got {offsets.dtype}")
+    if offsets.ndim != 6 or offsets.shape[-1] != 2:
+        raise RuntimeError("offsets must be (B, Q, G, L, K, 2)")
+    if not value.is_cuda:
+        raise RuntimeError("deformops_b200 kernels run on CUDA tensors only (there is no CPU path)")
+    if value.dtype not in DTYPE_CODES:
+        raise RuntimeError(f"unsupported value dtype {value.dtype}; use float32, float16 or bfloat16")
+    if attn.dtype != value.dtype:
+        raise RuntimeError(f"attention weights must have the value dtype {value.dtype}, got {attn.dtype}")
+    if shapes.dtype != torch.int64 or starts.dtype != torch.int64:
+        raise RuntimeError("spatial_shapes and level_start_index must be int64")
+    if ref.dtype != torch.float32:
+        raise RuntimeError(f"reference points must be float32, got {ref.dtype}")
+    for name, t in (("value", value), ("spatial_shapes", shapes), ("level_start_index", starts),
+                    ("reference_points", ref), ("offsets", offsets), ("attn", attn)):
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")
+        if t.device != value.device:
+            raise RuntimeError(f"{name} is on {t.device}, value on {value.device}")
+    B, S, G, D = value.shape
+    _, Q, _, L, K, _ = offsets.shape
+    if ref.ndim != 4 or tuple(ref.shape[:3]) != (B, Q, L) or ref.shape[3] not in (2, 4):
+        raise RuntimeError(f"reference points must be ({B}, {Q}, {L}, 2 or 4), got "
+                           f"{tuple(ref.shape)}")
+    return B, S, G, D, Q, L, K
+
+
+def _offsets_forward_cuda(value, spatial_shapes, level_start_index, reference_points, offsets,
+                          attn, softmax):
+    B, S, G, D, Q, L, K = _check_offsets_operands(value, spatial_shapes, level_start_index,
+                                                  reference_points, offsets, attn)
+    out = torch.empty((B, Q, G * D), dtype=value.dtype, device=value.device)
+    if B == 0 or Q == 0:
+        return out
+    shim = load_library()
+    value, reference_points, offsets, attn = map(_aligned, (value, reference_points, offsets, attn))
+    stream = torch.cuda.current_stream(value.device).cuda_stream
+    st = shim.forward_offsets(_ptr(value), _ptr(spatial_shapes), _ptr(level_start_index),
+                              _ptr(reference_points), reference_points.shape[3], _ptr(offsets),
+                              DTYPE_CODES[offsets.dtype], _ptr(attn), _ptr(out), B, S, G, D, Q, L,
+                              K, DTYPE_CODES[value.dtype], int(softmax), value.device.index,
+                              ctypes.c_void_p(stream))
+    if st != 0:
+        _raise(shim, st, "msda_b200_forward_offsets")
+    launch_counter.kernels += 1
+    return out
+
+
+def _offsets_backward_cuda(value, spatial_shapes, level_start_index, reference_points, offsets,
+                           attn, grad_output, softmax):
+    B, S, G, D, Q, L, K = _check_offsets_operands(value, spatial_shapes, level_start_index,
+                                                  reference_points, offsets, attn)
+    if grad_output.dtype != value.dtype or not grad_output.is_contiguous():
+        raise RuntimeError("grad_output must be contiguous and have the value dtype")
+    grad_value = torch.empty_like(value)
+    grad_offsets = torch.empty_like(offsets)
+    grad_attn = torch.empty_like(attn)
+    if B == 0:
+        return grad_value, grad_offsets, grad_attn
+    shim = load_library()
+    value, reference_points, offsets, attn, grad_output = map(
+        _aligned, (value, reference_points, offsets, attn, grad_output))
+    stream = torch.cuda.current_stream(value.device).cuda_stream
+    nbytes = shim.scratch_bytes(B, S, G, D, DTYPE_CODES[value.dtype]) if Q > 0 else 0
+    scratch = (torch.empty(nbytes // 4, dtype=torch.float32, device=value.device)
+               if nbytes else None)
+    st = shim.backward_offsets(
+        _ptr(value), _ptr(spatial_shapes), _ptr(level_start_index), _ptr(reference_points),
+        reference_points.shape[3], _ptr(offsets), DTYPE_CODES[offsets.dtype], _ptr(attn),
+        _ptr(grad_output), _ptr(grad_value), _ptr(grad_offsets), _ptr(grad_attn),
+        _ptr(scratch) if nbytes else None, nbytes, 0, B, S, G, D, Q, L, K,
+        DTYPE_CODES[value.dtype], int(softmax), 1, value.device.index, ctypes.c_void_p(stream))
+    if st != 0:
+        _raise(shim, st, "msda_b200_backward_offsets")
+    launch_counter.kernels += (3 if nbytes else 1) if Q > 0 else 0
+    launch_counter.memsets += 0 if nbytes else 1
+    return grad_value, grad_offsets, grad_attn
+
+
+def _offsets_forward_meta(value, spatial_shapes, level_start_index, reference_points, offsets,
+                          attn, softmax):
+    B, _, G, D = value.shape
+    return value.new_empty((B, offsets.shape[1], G * D))
+
+
+def _offsets_backward_meta(value, spatial_shapes, level_start_index, reference_points, offsets,
+                           attn, grad_output, softmax):
+    return (value.new_empty(value.shape), offsets.new_empty(offsets.shape),
+            attn.new_empty(attn.shape))
+
+
+def _offsets_setup_context(ctx: Any, inputs: tuple[Any, ...], output: Tensor) -> None:
+    ctx.softmax = inputs[6]
+    ctx.save_for_backward(*inputs[:6])
+
+
+def _make_offsets_autograd_backward(backward_op):
+    @once_differentiable
+    def backward(ctx: Any, grad_output: Tensor):
+        value, shapes, starts, ref, offsets, attn = ctx.saved_tensors
+        with torch.autocast("cuda", enabled=False):
+            grad_value, grad_offsets, grad_attn = backward_op(
+                value, shapes, starts, ref, offsets, attn,
+                grad_output.contiguous().type_as(value), ctx.softmax)
+        grad_ref = None
+        if ctx.needs_input_grad[3]:
+            if ref.shape[-1] != 2:
+                raise RuntimeError(
+                    "msda_offsets: no gradient is produced for 4-coordinate reference boxes; "
+                    "compute the locations in torch and call msda for that case")
+            # d(location)/d(reference) = 1 and location gradient = offset gradient * (W, H)
+            wh = shapes.flip(-1).to(torch.float32)
+            grad_ref = (grad_offsets.to(torch.float32)
+                        * wh[None, None, None, :, None, :]).sum(dim=(2, 4))
+        return grad_value, None, None, grad_ref, grad_offsets, grad_attn, None
+
+    return backward
+
+
+def _define_offsets_ops() -> None:
+    namespace = getattr(torch.ops, NAMESPACE)
+    fwd, bwd = OFFSETS_OPS
+    if hasattr(namespace, fwd):
+        return
+    torch.library.define(f"{NAMESPACE}::{fwd}", _OFFSETS_FORWARD_SCHEMA)
+    torch.library.define(f"{NAMESPACE}::{bwd}", _OFFSETS_BACKWARD_SCHEMA)
+    torch.library.impl(f"{NAMESPACE}::{fwd}", "CUDA")(_offsets_forward_cuda)
+    torch.library.impl(f"{NAMESPACE}::{bwd}", "CUDA")(_offsets_backward_cuda)
+    torch.library.register_fake(f"{NAMESPACE}::{fwd}")(_offsets_forward_meta)
+    torch.library.register_fake(f"{NAMESPACE}::{bwd}")(_offsets_backward_meta)
+    backward_op = getattr(getattr(torch.ops, NAMESPACE), bwd).default
+    torch.library.register_autograd(
+        f"{NAMESPACE}::{fwd}", _make_offsets_autograd_backward(backward_op),
+        setup_context=_offsets_setup_context)
+
+
 # --- public ops -------------------------------------------------------------------------------
 #: kept for the life of the process: a collected Library unregisters its operators
 _PUBLIC_LIBRARY: "torch.library.Library | None" = None
@@ -276,3 +436,4 @@ def _define_public_ops() -> None:
 
 
 _define_private_ops()
+_define_offsets_ops()

@@ -13,7 +13,9 @@ from .msda import (
     MSDAMethod,
     apply_msda_method,
     forward,
+    locations_from_offsets,
     msda,
+    msda_from_offsets,
     resolve_method,
     supports_context,
     unsupported_reason,
@@ -21,6 +23,6 @@ from .msda import (
 
 __all__ = [
     "Backend", "CudaBackend", "MSDABackend", "MSDAContext", "MSDAMethod", "Method",
-    "apply_msda_method", "forward", "msda", "resolve_method", "supports_context",
-    "unsupported_reason",
+    "apply_msda_method", "forward", "locations_from_offsets", "msda", "msda_from_offsets",
+    "resolve_method", "supports_context", "unsupported_reason",
 ]

@@ -27,7 +27,7 @@ from ..core.sanitize import check_msda_call
 
 __all__ = [
     "Backend", "MSDABackend", "MSDAContext", "MSDAMethod", "apply_msda_method", "forward",
-    "msda", "resolve_method", "supports_context",
+    "locations_from_offsets", "msda", "msda_from_offsets", "resolve_method", "supports_context",
 ]
 
 MSDAMethod = Method
@@ -262,6 +262,75 @@ class _MSDA:
 
 
 msda = _MSDA()
+
+
+def locations_from_offsets(reference_points: Tensor, offsets: Tensor,
+                           spatial_shapes: Tensor) -> Tensor:
+    """The layers' location arithmetic in torch (``sources/deformops/nn/msda.py:222-239``):
+    ``(B,Q,L,2|4)`` reference points and ``(B,Q,G,L,K,2)`` offsets -> ``(B,Q,G,L,K,2)``."""
+    ref = reference_points[:, :, None, :, None, :]
+    if reference_points.shape[-1] == 2:
+        wh = spatial_shapes.flip(-1).to(offsets.dtype)                # (L, 2) as (width, height)
+        return ref + offsets / wh[None, None, None, :, None, :]
+    if reference_points.shape[-1] == 4:
+        return ref[..., :2] + offsets / offsets.shape[4] * ref[..., 2:] * 0.5
+    raise ValueError("reference points must end in 2 or 4 coordinates, got "
+                     f"{reference_points.shape[-1]}")
+
+
+def msda_from_offsets(value: Tensor, spatial_shapes: Tensor, level_start_index: Tensor,
+                      reference_points: Tensor, offsets: Tensor, attention_weights: Tensor, *,
+                      method: "str | Method | None" = None, softmax: bool = False) -> Tensor:
+    """MSDA straight from what a deformable-attention layer predicts.
+
+    ``reference_points (B,Q,L,2|4)`` and ``offsets (B,Q,G,L,K,2)`` take the place of the
+    sampling locations; the kernels compute ``ref + offsets / (W, H)`` (two coordinates) or
+    ``ref.xy + offsets / K * ref.wh / 2`` (boxes) per point in float32, so the location
+    tensor and its gradient are never materialised.  Offsets may stay in the value dtype
+    (their gradient then comes back in it) or be float32.  Gradients flow to value, offsets
+    and weights, and to two-coordinate reference points; boxes that require a gradient take
+    the unfused route (locations in torch, then :data:`msda`).
+    """
+    resolved = resolve_method(method, softmax=softmax)
+    if reference_points.ndim != 4 or reference_points.shape[-1] not in (2, 4):
+        raise ValueError("reference points must be (B, Q, L, 2) or (B, Q, L, 4); got "
+                         f"{tuple(reference_points.shape)}")
+    if offsets.ndim == 6 and tuple(reference_points.shape[:3]) != (
+            offsets.shape[0], offsets.shape[1], offsets.shape[3]):
+        raise ValueError(f"reference points {tuple(reference_points.shape)} do not match offsets "
+                         f"{tuple(offsets.shape)} in batch, queries or levels")
+    check_msda_call(value, spatial_shapes, level_start_index, offsets, attention_weights)
+    if reference_points.device != value.device:
+        raise ValueError(f"reference points are on {reference_points.device}, value on "
+                         f"{value.device}")
+    context = MSDAContext.from_call(value, spatial_shapes, offsets, attention_weights, resolved)
+    reason = unsupported_reason(context)
+    if reason is not None:
+        raise NoBackendError(f"msda cannot run this call: {reason}")
+    if (reference_points.shape[-1] == 4 and reference_points.requires_grad
+            and torch.is_grad_enabled()):
+        locations = locations_from_offsets(reference_points.float(), offsets.float(),
+                                           spatial_shapes)
+        return msda(value, spatial_shapes, level_start_index, locations, attention_weights,
+                    method=resolved)
+
+    B, _, G, D = value.shape
+    Q = offsets.shape[1]
+    if Q == 0 or B == 0:
+        return value.new_zeros((B, Q, G * D))
+    load_library()
+    value = value.contiguous()
+    if offsets.dtype != value.dtype:
+        offsets = offsets.to(torch.float32)
+    weights = attention_weights.contiguous()
+    with torch.autocast("cuda", enabled=False):
+        out = torch.ops.deformops_b200.msda_offsets_forward(
+            value, spatial_shapes.to(torch.int64).contiguous(),
+            level_start_index.to(torch.int64).contiguous(),
+            reference_points.to(torch.float32).contiguous(), offsets.contiguous(),
+            weights.flatten(-2).type_as(value) if weights.ndim == 5 else weights.type_as(value),
+            resolved is Method.SOFTMAX)
+        return out.type_as(value)
 
 
 def _public_kernel(method: Method):

@@ -36,7 +36,7 @@
 extern "C" {
 #endif
 
-#define MSDA_B200_ABI_VERSION 3
+#define MSDA_B200_ABI_VERSION 4
 
 enum msda_b200_dtype { MSDA_B200_F32 = 0, MSDA_B200_F16 = 1, MSDA_B200_BF16 = 2 };
 
@@ -108,6 +108,42 @@ int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
  * Replaces: the `new_zeros` float32 grad_value of msda_launch.cuh:188-197.
  */
 int64_t msda_b200_backward_scratch_bytes(int64_t B, int64_t S, int64_t G, int64_t D, int dtype);
+
+/*
+ * Forward / backward with the caller's location arithmetic fused in.  Instead of a location
+ * tensor the call takes what a deformable-attention layer predicts and where it anchors it:
+ *   offsets           (B, Q, G, L, K, 2)  float32 or `dtype` (offsets_dtype says which)
+ *   reference_points  (B, Q, L, ref_coords) float32, 16-byte aligned;
+ *                     ref_coords = 2: (x, y) normalised;  4: a box (cx, cy, w, h)
+ * and samples at, in float32,
+ *   ref_coords = 2:  reference.xy + offset / (W_l, H_l)
+ *   ref_coords = 4:  reference.xy + offset / K * reference.wh * 0.5
+ * so the location tensor (the largest operand of the op) is never written or read.
+ * grad_offsets has the shape and element type of offsets and is written in full.  No gradient
+ * is produced for reference_points; for ref_coords = 2 it is the sum of
+ * grad_offsets * (W_l, H_l) over heads and points, which a caller can form from grad_offsets.
+ * Everything else (value, attn, scratch, status codes, stream and device) is as in
+ * msda_b200_forward / msda_b200_backward.
+ * Replaces: the elementwise location passes the reference's layers run in torch before the
+ * op and autograd runs after it (sources/deformops/nn/msda.py:222-239,
+ * sources/deformops/integrations/transformers.py:185-218) together with
+ * msda_launch.cuh:63-138 / :141-275.
+ */
+int msda_b200_forward_offsets(const void *value, const int64_t *spatial_shapes,
+                              const int64_t *level_start_index, const float *reference_points,
+                              int ref_coords, const void *offsets, int offsets_dtype,
+                              const void *attn, void *out, int64_t B, int64_t S, int64_t G,
+                              int64_t D, int64_t Q, int64_t L, int64_t K, int dtype,
+                              int apply_softmax, int device, void *stream);
+
+int msda_b200_backward_offsets(const void *value, const int64_t *spatial_shapes,
+                               const int64_t *level_start_index, const float *reference_points,
+                               int ref_coords, const void *offsets, int offsets_dtype,
+                               const void *attn, const void *grad_out, void *grad_value,
+                               void *grad_offsets, void *grad_attn, void *scratch,
+                               int64_t scratch_bytes, int64_t scratch_adds, int64_t B, int64_t S,
+                               int64_t G, int64_t D, int64_t Q, int64_t L, int64_t K, int dtype,
+                               int apply_softmax, int zero_grad_value, int device, void *stream);
 
 /*
  * Backward for callers that cannot allocate device memory (a runtime that handed all of it

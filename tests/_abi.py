@@ -61,5 +61,36 @@ def abi_backward(value, shapes, starts, loc, attn, grad_out, *, softmax=False, z
     return grad_value, grad_loc, grad_attn
 
 
+def abi_forward_offsets(value, shapes, starts, ref, offsets, attn, *, softmax=False):
+    shim = load_library()
+    B, S, G, D, Q, L, K = dims(value, offsets)
+    out = torch.full((B, Q, G * D), float("nan"), dtype=value.dtype, device=value.device)
+    s = torch.cuda.current_stream().cuda_stream
+    st = shim.forward_offsets(_p(value), _p(shapes), _p(starts), _p(ref), ref.shape[-1],
+                              _p(offsets), DTYPE_CODES[offsets.dtype], _p(attn), _p(out), B, S, G,
+                              D, Q, L, K, DTYPE_CODES[value.dtype], int(softmax),
+                              value.device.index, ctypes.c_void_p(s))
+    assert st == 0, shim.last_error()
+    return out
+
+
+def abi_backward_offsets(value, shapes, starts, ref, offsets, attn, grad_out, *, softmax=False):
+    shim = load_library()
+    B, S, G, D, Q, L, K = dims(value, offsets)
+    grad_value = torch.full_like(value, float("nan"))
+    grad_offsets = torch.full_like(offsets, float("nan"))
+    grad_attn = torch.full_like(attn, float("nan"))
+    nbytes = shim.scratch_bytes(B, S, G, D, DTYPE_CODES[value.dtype])
+    buf = torch.full((max(nbytes // 4, 1),), float("nan"), device=value.device) if nbytes else None
+    s = torch.cuda.current_stream().cuda_stream
+    st = shim.backward_offsets(_p(value), _p(shapes), _p(starts), _p(ref), ref.shape[-1],
+                               _p(offsets), DTYPE_CODES[offsets.dtype], _p(attn), _p(grad_out),
+                               _p(grad_value), _p(grad_offsets), _p(grad_attn), _p(buf), nbytes, 0,
+                               B, S, G, D, Q, L, K, DTYPE_CODES[value.dtype], int(softmax), 1,
+                               value.device.index, ctypes.c_void_p(s))
+    assert st == 0, shim.last_error()
+    return grad_value, grad_offsets, grad_attn
+
+
 def to_np(t):
     return t.detach().float().cpu().numpy().astype(np.float64)
