@@ -64,6 +64,8 @@ def parse():
     ap.add_argument("--no-scratch", action="store_true",
                     help="backward without the replica scratch (every level adds straight into grad_value)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-caller-path", action="store_true",
+                    help="skip the leg that times the layer-level call (fused vs torch arithmetic)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0,
                     help="target CPU time of the cpu_baseline sample")
     return ap.parse_args()
@@ -369,6 +371,52 @@ def main():
         d2h = sum(t.numel() * t.element_size() for t in sink.values())
         e2e = {"ms": e2e_ms, "h2d": h2d, "d2h": d2h, "steps": e2e_steps}
 
+    # ---- caller path: what a deformable-attention layer does around the operator -------------
+    # Same sampling pattern, expressed the way a layer holds it: raw logits, reference points
+    # and offsets in the value dtype.  (a) torch computes softmax and ref + offsets / (W, H),
+    # then the linear operator runs (what the reference's Hugging Face module does);
+    # (b) one fused call.  Forward + backward through autograd, resident inputs.
+    caller = None
+    if world == 1 and not args.no_caller_path:
+        from deformops_b200.registry import locations_from_offsets, msda_from_offsets
+
+        d0 = sets[0][2]
+        gen = torch.Generator(device=device).manual_seed(1)
+        ref = torch.rand((Bq, Q, L, 2), device=device, generator=gen)
+        wh = d0["shapes"].flip(-1).to(torch.float32)[None, None, None, :, None, :]
+        offsets = ((d0["sampling_locations"] - ref[:, :, None, :, None, :]) * wh).to(w0.value.dtype)
+        leaves = [d0["value"].detach().clone().requires_grad_(),
+                  offsets.requires_grad_(),
+                  d0["attention_weights"].detach().clone().requires_grad_()]
+
+        def torch_arithmetic():
+            v, off, logits = leaves
+            weights = torch.softmax(logits, -1)
+            loc = locations_from_offsets(ref, off, d0["shapes"])
+            return msda(v, d0["shapes"], d0["starts"], loc, weights)
+
+        def fused():
+            v, off, logits = leaves
+            return msda_from_offsets(v, d0["shapes"], d0["starts"], ref, off, logits, softmax=True)
+
+        caller = {}
+        for name, fn in (("torch_arithmetic_ms", torch_arithmetic), ("fused_ms", fused)):
+            n = max(3, min(args.steps, 20))
+            for _ in range(3):
+                torch.autograd.grad(fn(), leaves, d0["grad_output"])
+            torch.cuda.synchronize()
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            c0.record(stream)
+            for _ in range(n):
+                torch.autograd.grad(fn(), leaves, d0["grad_output"])
+            c1.record(stream)
+            torch.cuda.synchronize()
+            caller[name] = c0.elapsed_time(c1) / n
+        caller["what"] = ("fwd+bwd of softmax + location arithmetic + operator, offsets in the "
+                          "value dtype; torch_arithmetic = elementwise passes in torch around "
+                          "the linear operator, fused = one msda_from_offsets call")
+        del leaves, offsets, ref
+
     # ---- max over ranks -------------------------------------------------------------------
     stats = torch.tensor([ms_total, fwd_ms, bwd_ms, e2e["ms"] if e2e else 0.0],
                          device=device, dtype=torch.float64)
@@ -425,6 +473,8 @@ def main():
                            "pipeline": ("whole batch, no overlap" if args.e2e_sequential else
                                         "per-sample chunks; upload, kernels and download on "
                                         "three streams")}
+        if caller:
+            line["caller_path"] = caller
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_eager_sample(args.workload, args.cpu_seconds)
         print(json.dumps(line), flush=True)
