@@ -21,7 +21,7 @@ CSRC = PKG / "csrc"
 LIB_DIR = PKG / "_lib"
 LIB_PATH = LIB_DIR / "libmsda_b200.so"
 SOURCES = ["msda_forward.cu", "msda_backward.cu", "msda_abi.cu", "msda_static_scratch.cu",
-           "msda_l2_window.cu", "msda_backward_region.cu"]
+           "msda_l2_window.cu", "msda_backward_region.cu", "msda_f64.cu"]
 HEADERS = [CSRC / "msda_common.cuh", PKG.parent / "include" / "msda_b200.h"]
 
 NVCC_FLAGS = [

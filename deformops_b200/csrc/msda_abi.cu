@@ -22,22 +22,26 @@ int fail(int status, const char *fmt, ...) {
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-int element_size(int dtype) { return dtype == MSDA_B200_F32 ? 4 : 2; }
+int element_size(int dtype) {
+    return dtype == MSDA_B200_F64 ? 8 : dtype == MSDA_B200_F32 ? 4 : 2;
+}
 
 constexpr size_t kSmemBudget = 96 * 1024;   // per CTA, so that at least two CTAs share an SM
 
 // Shape checks shared by forward, backward and the geometry query; fills the launch plan.
 int plan(msda_b200::Params &p, int64_t B, int64_t S, int64_t G, int64_t D, int64_t Q, int64_t L,
          int64_t K, int dtype, bool softmax) {
-    if (dtype != MSDA_B200_F32 && dtype != MSDA_B200_F16 && dtype != MSDA_B200_BF16)
-        return fail(MSDA_B200_INVALID_ARGUMENT, "dtype %d is not f32(0), f16(1) or bf16(2)", dtype);
+    if (dtype != MSDA_B200_F32 && dtype != MSDA_B200_F16 && dtype != MSDA_B200_BF16 &&
+        dtype != MSDA_B200_F64)
+        return fail(MSDA_B200_INVALID_ARGUMENT,
+                    "dtype %d is not f32(0), f16(1), bf16(2) or f64(3)", dtype);
     if (B < 0 || S < 0 || Q < 0 || G <= 0 || D <= 0 || L <= 0 || K <= 0)
         return fail(MSDA_B200_INVALID_ARGUMENT,
                     "sizes must satisfy B,S,Q >= 0 and G,D,L,K > 0 (got B=%lld S=%lld G=%lld "
                     "D=%lld Q=%lld L=%lld K=%lld)",
                     (long long)B, (long long)S, (long long)G, (long long)D, (long long)Q,
                     (long long)L, (long long)K);
-    const int vec = 16 / element_size(dtype);
+    const int vec = dtype == MSDA_B200_F64 ? 1 : 16 / element_size(dtype);
     if (D % vec != 0)
         return fail(MSDA_B200_UNSUPPORTED,
                     "head dimension D=%lld must be a multiple of %d for this dtype (16-byte "
@@ -59,6 +63,16 @@ int plan(msda_b200::Params &p, int64_t B, int64_t S, int64_t G, int64_t D, int64
     p.D = (int)D;
     p.L = (int)L;
     p.K = (int)K;
+    if (dtype == MSDA_B200_F64) {
+        // the float64 kernels (msda_f64.cu) run a warp per (query, head) pair, no staging
+        p.lph_log2 = 5;
+        p.point_chunk = (int)(L * K);
+        p.threads = 256;
+        p.num_groups = B * Q * G;
+        const int64_t grid = (p.num_groups + 7) / 8;
+        p.grid = (unsigned)(grid > 148 * 64 ? 148 * 64 : grid);
+        return MSDA_B200_OK;
+    }
     const int lanes = (int)(D / vec);
     int lg = 0;
     while ((1 << lg) < lanes && lg < 5) ++lg;
@@ -124,6 +138,9 @@ int check_points(const Points &pts, int offsets_dtype, int dtype, const char *wh
         return fail(MSDA_B200_INVALID_ARGUMENT,
                     "%s: reference points carry %d coordinates; 2 (x, y) or 4 (cx, cy, w, h) "
                     "are supported", who, pts.ref_coords);
+    if (dtype == MSDA_B200_F64)
+        return fail(MSDA_B200_UNSUPPORTED,
+                    "%s: float64 values take locations (msda_b200_forward / _backward)", who);
     if (offsets_dtype != MSDA_B200_F32 && offsets_dtype != dtype)
         return fail(MSDA_B200_INVALID_ARGUMENT,
                     "%s: offsets must be float32 or the value dtype (got %d for value dtype %d)",
@@ -168,8 +185,9 @@ int msda_b200_launch_geometry(int64_t B, int64_t G, int64_t D, int64_t Q, int64_
     if (st != MSDA_B200_OK) return st;
     if (grid) *grid = p.grid;
     if (threads) *threads = p.threads;
-    if (smem_fwd) *smem_fwd = (int64_t)msda_b200::forward_smem_bytes(p, apply_softmax != 0);
-    if (smem_bwd) *smem_bwd = (int64_t)msda_b200::backward_smem_bytes(p, apply_softmax != 0);
+    const bool f64 = dtype == MSDA_B200_F64;   // those kernels use no dynamic shared memory
+    if (smem_fwd) *smem_fwd = f64 ? 0 : (int64_t)msda_b200::forward_smem_bytes(p, apply_softmax != 0);
+    if (smem_bwd) *smem_bwd = f64 ? 0 : (int64_t)msda_b200::backward_smem_bytes(p, apply_softmax != 0);
     return MSDA_B200_OK;
 }
 
@@ -261,7 +279,10 @@ int forward_impl(const void *value, const int64_t *spatial_shapes, const int64_t
     DeviceGuard guard(device);
     if (guard.err != cudaSuccess) return cuda_fail(guard.err, "forward: selecting the device");
     const cudaError_t e =
-        msda_b200::launch_forward(p, dtype, apply_softmax != 0, static_cast<cudaStream_t>(stream));
+        dtype == MSDA_B200_F64
+            ? msda_b200::launch_forward_f64(p, apply_softmax != 0, static_cast<cudaStream_t>(stream))
+            : msda_b200::launch_forward(p, dtype, apply_softmax != 0,
+                                        static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(e, "forward: kernel launch");
     return MSDA_B200_OK;
 }
@@ -279,7 +300,8 @@ int backward_impl(const void *value, const int64_t *spatial_shapes,
     if (st != MSDA_B200_OK) return st;
     if (B == 0) return MSDA_B200_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const bool use_scratch = scratch != nullptr && dtype != MSDA_B200_F32 && S > 0 && Q > 0;
+    const bool use_scratch = scratch != nullptr &&
+                             (dtype == MSDA_B200_F16 || dtype == MSDA_B200_BF16) && S > 0 && Q > 0;
     if (use_scratch) {
         if (!zero_grad_value)
             return fail(MSDA_B200_INVALID_ARGUMENT,
@@ -339,7 +361,9 @@ int backward_impl(const void *value, const int64_t *spatial_shapes,
         const char *v = std::getenv("MSDA_B200_REGION_BACKWARD");
         return v != nullptr && (v[0] == '1' || v[0] == '2') ? v[0] - '0' : 0;
     }();
-    if (region_mode && msda_b200::backward_region_eligible(p, dtype, apply_softmax != 0))
+    if (dtype == MSDA_B200_F64)
+        e = msda_b200::launch_backward_f64(p, apply_softmax != 0, s);
+    else if (region_mode && msda_b200::backward_region_eligible(p, dtype, apply_softmax != 0))
         e = msda_b200::launch_backward_region(p, dtype, apply_softmax != 0, region_mode == 1, s);
     else
         e = msda_b200::launch_backward(p, dtype, apply_softmax != 0, s);

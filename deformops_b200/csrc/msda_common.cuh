@@ -414,6 +414,9 @@ cudaError_t launch_forward(const Params &p, int dtype, bool softmax, cudaStream_
 cudaError_t launch_backward(const Params &p, int dtype, bool softmax, cudaStream_t stream);
 cudaError_t launch_prepare_grad_value(const Params &p, int dtype, cudaStream_t stream);
 cudaError_t launch_finalize_grad_value(const Params &p, int dtype, cudaStream_t stream);
+// float64 kernels (msda_f64.cu): loc / grad_loc point at doubles
+cudaError_t launch_forward_f64(const Params &p, bool softmax, cudaStream_t stream);
+cudaError_t launch_backward_f64(const Params &p, bool softmax, cudaStream_t stream);
 size_t forward_smem_bytes(const Params &p, bool softmax);
 size_t backward_smem_bytes(const Params &p, bool softmax);
 // region-tiled backward for encoder calls (msda_backward_region.cu)

@@ -61,7 +61,7 @@ PRIVATE_OPS = ("msda_forward", "msda_backward", "msda_softmax_forward", "msda_so
 PUBLIC_OPS = ("msda", "msda_softmax")
 
 #: dtype codes of ``enum msda_b200_dtype``
-DTYPE_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+DTYPE_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2, torch.float64: 3}
 
 _FORWARD_INPUTS = 9
 
@@ -96,9 +96,13 @@ def _check_operands(value: Tensor, shapes: Tensor, starts: Tensor, loc: Tensor, 
     if not value.is_cuda:
         raise RuntimeError("deformops_b200 kernels run on CUDA tensors only (there is no CPU path)")
     if value.dtype not in DTYPE_CODES:
-        raise RuntimeError(f"unsupported value dtype {value.dtype}; use float32, float16 or bfloat16")
-    if loc.dtype != torch.float32:
-        raise RuntimeError(f"sampling locations must be float32, got {loc.dtype}")
+        raise RuntimeError(f"unsupported value dtype {value.dtype}; use float32, float16, "
+                           "bfloat16 or float64")
+    # float64 values come with float64 locations (the gradcheck configuration)
+    loc_dtype = torch.float64 if value.dtype == torch.float64 else torch.float32
+    if loc.dtype != loc_dtype:
+        raise RuntimeError(f"sampling locations must be {loc_dtype} for {value.dtype} values, "
+                           f"got {loc.dtype}")
     if attn.dtype != value.dtype:
         raise RuntimeError(f"attention weights must have the value dtype {value.dtype}, got {attn.dtype}")
     if shapes.dtype != torch.int64 or starts.dtype != torch.int64:
@@ -258,7 +262,7 @@ def _check_offsets_operands(value: Tensor, shapes: Tensor, starts: Tensor, ref: 
         raise RuntimeError("offsets must be (B, Q, G, L, K, 2)")
     if not value.is_cuda:
         raise RuntimeError("deformops_b200 kernels run on CUDA tensors only (there is no CPU path)")
-    if value.dtype not in DTYPE_CODES:
+    if value.dtype not in DTYPE_CODES or value.dtype == torch.float64:
         raise RuntimeError(f"unsupported value dtype {value.dtype}; use float32, float16 or bfloat16")
     if attn.dtype != value.dtype:
         raise RuntimeError(f"attention weights must have the value dtype {value.dtype}, got {attn.dtype}")

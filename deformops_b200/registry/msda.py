@@ -92,7 +92,8 @@ class MSDABackend(Protocol):
                 method: Method) -> Tensor: ...
 
 
-_VECTOR = {torch.float32: 4, torch.float16: 8, torch.bfloat16: 8}
+#: channels per 16-byte vector; float64 runs on the simple gradcheck kernels (any head size)
+_VECTOR = {torch.float32: 4, torch.float16: 8, torch.bfloat16: 8, torch.float64: 1}
 _MAX_LEVELS = 16
 
 
@@ -104,7 +105,7 @@ def unsupported_reason(context: MSDAContext) -> str | None:
         return (f"device has compute capability {context.sm_version[0]}.{context.sm_version[1]}; "
                 "the kernels are built for sm_100a only")
     if context.dtype not in _VECTOR:
-        return f"dtype {context.dtype} is not float32, float16 or bfloat16"
+        return f"dtype {context.dtype} is not float32, float16, bfloat16 or float64"
     if context.head_dim and context.head_dim % _VECTOR[context.dtype] != 0:
         return (f"head dimension {context.head_dim} is not a multiple of "
                 f"{_VECTOR[context.dtype]} (16-byte channel vectors)")
@@ -141,7 +142,8 @@ def forward(value: Tensor, spatial_shapes: Tensor, level_start_index: Tensor,
 
     Makes operands kernel-ready the way the reference's functional entry does
     (``_msda_bridge.py:411-448``): contiguous tensors, int64 level tables (converted on the
-    device, no host synchronisation), float32 locations, weights in the value dtype, autocast
+    device, no host synchronisation), float32 locations (float64 for float64 values), weights
+    in the value dtype, autocast
     disabled around the op; empty batch or zero queries return zeros without a launch.
     The weights may be ``(B,Q,G,L*K)`` or ``(B,Q,G,L,K)``; their gradient comes back in the
     shape and dtype given.
@@ -166,7 +168,9 @@ def forward(value: Tensor, spatial_shapes: Tensor, level_start_index: Tensor,
           else torch.ops.deformops_b200.msda_forward)
     with torch.autocast("cuda", enabled=False):
         result = op(value, spatial_shapes, level_start_index,
-                    sampling_locations.to(torch.float32), attention_weights.type_as(value),
+                    sampling_locations.to(torch.float64 if value.dtype == torch.float64
+                                          else torch.float32),
+                    attention_weights.type_as(value),
                     chunk_step, num_points, channels_per_thread, threads_per_block)
         return result.type_as(value)
 
@@ -307,9 +311,12 @@ def msda_from_offsets(value: Tensor, spatial_shapes: Tensor, level_start_index: 
     reason = unsupported_reason(context)
     if reason is not None:
         raise NoBackendError(f"msda cannot run this call: {reason}")
-    if (reference_points.shape[-1] == 4 and reference_points.requires_grad
-            and torch.is_grad_enabled()):
-        locations = locations_from_offsets(reference_points.float(), offsets.float(),
+    needs_box_gradient = (reference_points.shape[-1] == 4 and reference_points.requires_grad
+                          and torch.is_grad_enabled())
+    if needs_box_gradient or value.dtype == torch.float64:
+        # float64 (numerical differentiation) runs on the location kernels only
+        work = torch.float64 if value.dtype == torch.float64 else torch.float32
+        locations = locations_from_offsets(reference_points.to(work), offsets.to(work),
                                            spatial_shapes)
         return msda(value, spatial_shapes, level_start_index, locations, attention_weights,
                     method=resolved)

@@ -23,7 +23,8 @@
  *     longjmp ever crosses the boundary.
  *   - Thread safety: no mutable global state; concurrent calls from several host
  *     threads (for example the autograd thread) are allowed.
- *   - Supported: dtype f32 / f16 / bf16; D a multiple of 4 (f32) or 8 (f16, bf16);
+ *   - Supported: dtype f32 / f16 / bf16 (and f64, see the enum); D a multiple of 4 (f32) or
+ *     8 (f16, bf16);
  *     1 <= L <= 16; any K >= 1; S*G*D < 2^31 per sample.  B == 0 or Q == 0 is a
  *     successful no-op (backward still clears grad_value).
  */
@@ -38,7 +39,13 @@ extern "C" {
 
 #define MSDA_B200_ABI_VERSION 4
 
-enum msda_b200_dtype { MSDA_B200_F32 = 0, MSDA_B200_F16 = 1, MSDA_B200_BF16 = 2 };
+/*
+ * MSDA_B200_F64: value, attn, out AND loc / grad_loc are double (pass the double pointers
+ * through the `float *` parameters).  Meant for numerical differentiation
+ * (torch.autograd.gradcheck), as in the reference (msda_launch.cuh:54-61); simple kernels, any
+ * D >= 1, no scratch, not available through the *_offsets entry points.
+ */
+enum msda_b200_dtype { MSDA_B200_F32 = 0, MSDA_B200_F16 = 1, MSDA_B200_BF16 = 2, MSDA_B200_F64 = 3 };
 
 enum msda_b200_status {
     MSDA_B200_OK = 0,

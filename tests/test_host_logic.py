@@ -124,7 +124,8 @@ def test_context_and_supports():
     assert supports_context(gpu)
     assert "sm_100a" in unsupported_reason(dataclasses.replace(gpu, sm_version=(9, 0)))
     assert "multiple" in unsupported_reason(dataclasses.replace(gpu, head_dim=6))
-    assert "float64" in unsupported_reason(dataclasses.replace(gpu, dtype=torch.float64))
+    assert supports_context(dataclasses.replace(gpu, dtype=torch.float64, head_dim=3))
+    assert "int32" in unsupported_reason(dataclasses.replace(gpu, dtype=torch.int32))
     assert "levels" in unsupported_reason(dataclasses.replace(gpu, num_levels=17))
     # num_queries is not part of equality (varying resolutions share one context)
     assert dataclasses.replace(gpu, num_queries=7) == gpu and isinstance(gpu, MSDAContext)
