@@ -2,6 +2,8 @@
 
 from __future__ import annotations
 
+import pathlib
+
 import numpy as np
 import pytest
 import torch
@@ -247,3 +249,49 @@ def test_export_and_dynamo_record_the_public_op():
     assert any("deformops_b200.msda_softmax" in x for x in seen), seen
     fewer = (t["value"], t["shapes"], t["starts"], t["loc"][:, :5], t["attn_linear"][:, :5])
     assert torch.equal(compiled(*fewer), Layer()(*fewer))
+
+
+def test_aot_inductor_package_runs_in_a_fresh_process(tmp_path, monkeypatch):
+    """An AOTInductor package of a module that calls the operator runs in a new process once
+    that process has imported the package (which registers the ops and their CUDA
+    implementations) - the recipe the reference documents for its CUDA operators
+    (``docs/export.md``: "needs their library loaded first")."""
+    import shutil
+    import subprocess
+    import sys
+
+    from deformops_b200.registry import msda
+
+    # Inductor compiles its wrapper with $CXX; use the system compiler found on PATH (an
+    # environment may point CXX at a toolchain without OpenMP support files)
+    if shutil.which("g++"):
+        monkeypatch.setenv("CXX", shutil.which("g++"))
+
+    _, t = _case("small_b")
+    args = (t["value"], t["shapes"], t["starts"], t["loc"], t["attn_linear"])
+
+    class Layer(torch.nn.Module):
+        def forward(self, value, shapes, starts, loc, attn):
+            return msda(value, shapes, starts, loc, attn, method="softmax") * 2.0
+
+    expected = Layer()(*args)
+    exported = torch.export.export(Layer(), args)
+    package = torch._inductor.aoti_compile_and_package(
+        exported, package_path=str(tmp_path / "layer.pt2"))
+    torch.save({"args": [a.cpu() for a in args], "expected": expected.cpu()},
+               tmp_path / "io.pt")
+    script = (
+        "import sys, torch\n"
+        "import deformops_b200\n"
+        f"io = torch.load(r'{tmp_path / 'io.pt'}')\n"
+        f"runner = torch._inductor.aoti_load_package(r'{package}')\n"
+        "out = runner(*[a.cuda() for a in io['args']])\n"
+        "torch.cuda.synchronize()\n"
+        "assert torch.equal(out.cpu(), io['expected']), (out.cpu() - io['expected']).abs().max()\n"
+        "from deformops_b200._loader import loaded\n"
+        "assert loaded()\n"
+        "print('aoti-ok')\n")
+    root = pathlib.Path(__file__).resolve().parents[1]
+    done = subprocess.run([sys.executable, "-c", script], cwd=root, capture_output=True,
+                          text=True, timeout=600)
+    assert done.returncode == 0 and "aoti-ok" in done.stdout, done.stderr[-2000:]
