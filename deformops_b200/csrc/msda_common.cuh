@@ -199,12 +199,18 @@ __device__ __forceinline__ uint4 ldg16(const void *p) {
     return __ldg(reinterpret_cast<const uint4 *>(p));
 }
 
+// load instruction of the backward's corner gather (a tuning knob: cache operators and
+// eviction hints can be swapped in at compile time)
+#ifndef MSDA_BWD_GATHER_LD
+#define MSDA_BWD_GATHER_LD "ld.global.nc.v4.u32"
+#endif
+
 // Read-only 16-byte gather load, predicated: returns zeros and touches no memory when
 // `pred` is false.  Not volatile, so the compiler may batch the loads of several points.
 __device__ __forceinline__ uint4 ldg16_if(const void *p, bool pred) {
     uint4 r;
     asm("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %5, 0;\n\tmov.u32 %0, 0;\n\tmov.u32 %1, 0;\n\t"
-        "mov.u32 %2, 0;\n\tmov.u32 %3, 0;\n\t@q ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];\n\t}"
+        "mov.u32 %2, 0;\n\tmov.u32 %3, 0;\n\t@q " MSDA_BWD_GATHER_LD " {%0, %1, %2, %3}, [%4];\n\t}"
         : "=&r"(r.x), "=&r"(r.y), "=&r"(r.z), "=&r"(r.w)
         : "l"(p), "r"((unsigned)pred));
     return r;

@@ -25,13 +25,15 @@ pytestmark = pytest.mark.gpu
 
 TOL = {torch.float32: (1e-5, 1e-4), torch.float16: (1e-2, 1e-2), torch.bfloat16: (1e-2, 1e-2)}
 DTYPES = [torch.float32, torch.float16, torch.bfloat16]
-_LOG = pathlib.Path(os.environ.get("GRAFT_REPO_ROOT", pathlib.Path(__file__).resolve().parents[1])) \
-    / "gpurun_out" / "parity_errors.jsonl"
+#: set DEFORMOPS_B200_PARITY_LOG to a file to collect the measured errors of every case
+_LOG = os.environ.get("DEFORMOPS_B200_PARITY_LOG")
 
 
 def _record(name, dtype, method, errs):
+    if not _LOG:
+        return
     try:
-        _LOG.parent.mkdir(exist_ok=True)
+        pathlib.Path(_LOG).parent.mkdir(parents=True, exist_ok=True)
         with open(_LOG, "a") as fh:
             fh.write(json.dumps({"case": name, "dtype": str(dtype), "method": method,
                                  **{k: float(v) for k, v in errs.items()}}) + "\n")
