@@ -309,8 +309,11 @@ def main():
         abi_step(sets[i % NUM_SETS][2], evs[i])
         evs[i][2].record(stream)
     barrier()
-    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
-    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
+    fwd_all = [e[0].elapsed_time(e[1]) for e in evs]
+    bwd_all = [e[1].elapsed_time(e[2]) for e in evs]
+    fwd_ms, bwd_ms = statistics.mean(fwd_all), statistics.mean(bwd_all)
+    spread = {"forward_median": statistics.median(fwd_all), "forward_min": min(fwd_all),
+              "backward_call_median": statistics.median(bwd_all), "backward_call_min": min(bwd_all)}
 
     # ---- e2e: public operator, host buffers, copies inside the timed region --------------
     e2e = None
@@ -453,7 +456,7 @@ def main():
                        "parallelism": f"batch-sharded x{world}, no collective"},
             "clocks": clock_summary,
             "gpu_launches": (4 if nscratch else 2) * args.steps,
-            "kernels_ms": {"forward": fwd_ms, "backward_call": bwd_ms,
+            "kernels_ms": {"forward": fwd_ms, "backward_call": bwd_ms, **spread,
                            "backward_call_launches": ("prepare + backward + finalize kernels"
                                                       if nscratch else "memset + backward kernel")},
             "roofline": {"bound": "hbm", "kernel": "msda backward (whole call, grad_value clear included)", "achieved": achieved,
