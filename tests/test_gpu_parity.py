@@ -290,3 +290,47 @@ def test_bad_arguments_return_status_not_crash():
     assert st == -2
     st = shim.forward(null, null, null, null, null, null, 1, 4, 1, 8, 1, 1, 1, 7, 0, 0, null)
     assert st == -1
+
+
+def _random_shape_case():
+    """Hypothesis strategy over the operator's envelope, in the spirit of the reference's
+    property tests (``tests/deformops/test_msda_cuda.py:30-71``): ragged level pyramids down to
+    1x1, 1..8 points, 1..5 levels, odd head counts, head sizes from one to many 16-byte vectors,
+    locations reaching outside [0, 1]."""
+    from hypothesis import strategies as st
+
+    level = st.tuples(st.integers(1, 11), st.integers(1, 11))
+    return st.fixed_dictionaries({
+        "B": st.integers(1, 3), "G": st.integers(1, 9),
+        "D": st.sampled_from([4, 8, 12, 16, 32, 40, 64, 128]),
+        "levels": st.lists(level, min_size=1, max_size=5),
+        "K": st.integers(1, 8), "Q": st.integers(1, 70),
+        "spread": st.sampled_from([1.0, 1.3, 3.0]),
+        "softmax": st.booleans(), "seed": st.integers(0, 2**31 - 1),
+    })
+
+
+def test_random_envelope_float32_property():
+    from hypothesis import HealthCheck, given, settings
+
+    @settings(max_examples=120, deadline=None, derandomize=True,
+              suppress_health_check=list(HealthCheck))
+    @given(_random_shape_case())
+    def check(s):
+        g = torch.Generator().manual_seed(s["seed"])
+        levels = s["levels"]
+        L, S = len(levels), sum(h * w for h, w in levels)
+        B, G, D, K, Q = s["B"], s["G"], s["D"], s["K"], s["Q"]
+        shapes = torch.tensor(levels, dtype=torch.int64)
+        sizes = shapes[:, 0] * shapes[:, 1]
+        starts = torch.cumsum(sizes, 0) - sizes
+        value = torch.randn(B, S, G, D, generator=g)
+        loc = (torch.rand(B, Q, G, L, K, 2, generator=g) - 0.5) * s["spread"] + 0.5
+        logits = torch.randn(B, Q, G, L * K, generator=g)
+        grad_out = torch.randn(B, Q, G * D, generator=g)
+        method = "softmax" if s["softmax"] else "linear"
+        attn = logits if s["softmax"] else logits.softmax(-1)
+        run_case(f"property{(B, G, D, levels, K, Q)}", value, shapes, starts, loc, attn,
+                 grad_out, torch.float32, method)
+
+    check()
