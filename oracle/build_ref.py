@@ -10,7 +10,8 @@ are never copied; only the resulting ``.so`` files (git-ignored) are written, un
     msda_half2atomic.so   its native 16-bit-atomics configuration
 
 Flags follow ``sources/deformops/core/configs.py:48-66`` (``--use_fast_math``, C++20, the
-half-operator undefines, ``-DDEFORMOPS_NO_FP64`` as in its ahead-of-time build).  The
+half-operator undefines; ``-DDEFORMOPS_NO_FP64`` as in its ahead-of-time build for the
+16-bit configuration only, so that the production one also runs in float64).  The
 libraries are used by ``oracle/ref_cuda.py`` as the GPU-side parity oracle and speed bar.
 
     python oracle/build_ref.py [--reference /path/to/reference]
@@ -30,6 +31,9 @@ UNITS = {
     "msda_fp32acc": "sources/deformops/backends/cuda/msda_fp32acc.cu",
     "msda_half2atomic": "sources/deformops/backends/cuda/experimental/msda_half2atomic.cu",
 }
+#: the production configuration is built WITH double precision (the float64 parity test runs
+#: the reference's kernels in float64); the 16-bit-atomics one never sees float64
+NO_FP64 = {"msda_half2atomic": ["-DDEFORMOPS_NO_FP64"]}
 
 
 def build(reference: pathlib.Path, force: bool = False) -> list[pathlib.Path]:
@@ -52,7 +56,7 @@ def build(reference: pathlib.Path, force: bool = False) -> list[pathlib.Path]:
         cmd = [
             nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++20",
             "--use_fast_math", "-DUSE_CUDA", "-DTORCH_TARGET_VERSION=0x020B000000000000",
-            "-DDEFORMOPS_NO_FP64", "-U__CUDA_NO_HALF_OPERATORS__",
+            *NO_FP64.get(name, []), "-U__CUDA_NO_HALF_OPERATORS__",
             "-U__CUDA_NO_HALF_CONVERSIONS__", "-U__CUDA_NO_HALF2_OPERATORS__",
             "-Xcompiler", "-fPIC", "-shared", f"-I{include}",
             *[f"-I{p}" for p in cpp_extension.include_paths("cuda")],

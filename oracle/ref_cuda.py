@@ -55,24 +55,31 @@ def _op(prefix: str, softmax: bool, direction: str):
     return getattr(getattr(torch.ops, _NS), f"{prefix}{'_softmax' if softmax else ''}_{direction}")
 
 
+def _loc_for(value, loc):
+    """Locations as the reference's op wants them: float32, or float64 beside float64 values
+    (``msda_launch.cuh:54-61``)."""
+    return loc.to(torch.float64 if value.dtype == torch.float64 else torch.float32).contiguous()
+
+
 def forward(value, shapes, starts, loc, attn, *, softmax=False, prefix="msda_fp32acc",
             chunk_step=128):
     K = loc.shape[4]
     with torch.autocast("cuda", enabled=False):
         return _op(prefix, softmax, "forward")(
             value.contiguous(), shapes.to(torch.int64), starts.to(torch.int64),
-            loc.float().contiguous(), attn.contiguous().type_as(value), chunk_step, K, 0, 0)
+            _loc_for(value, loc), attn.contiguous().type_as(value), chunk_step, K, 0, 0)
 
 
 def backward(value, shapes, starts, loc, attn, grad_out, *, softmax=False,
              prefix="msda_fp32acc", chunk_step=128):
     """Gradients ``(grad_value, grad_loc, grad_attn)`` in the dtypes of the inputs."""
     K = loc.shape[4]
-    upcast = prefix == "msda_fp32acc"
+    # the production configuration upcasts 16-bit operands to float32; float64 stays float64
+    upcast = prefix == "msda_fp32acc" and value.dtype != torch.float64
     cast = (lambda t: t.float()) if upcast else (lambda t: t)
     with torch.autocast("cuda", enabled=False):
         gv, gl, ga = _op(prefix, softmax, "backward")(
             cast(value.contiguous()), shapes.to(torch.int64), starts.to(torch.int64),
-            cast(loc.float().contiguous()), cast(attn.contiguous()),
+            _loc_for(value, loc), cast(attn.contiguous()),
             cast(grad_out.contiguous()), chunk_step, K, 0, 0)
     return gv.type_as(value), gl.type_as(loc), ga.type_as(attn)

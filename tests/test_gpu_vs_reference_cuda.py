@@ -64,3 +64,24 @@ def test_fp32_against_reference_cuda(name, softmax):
 def test_16bit_against_reference_cuda_fp32_result(name, dtype):
     _, t = _inputs(name, dtype)
     _compare(t, dtype, False, 1e-2, 1e-2)
+
+
+@pytest.mark.parametrize("softmax", [False, True])
+def test_float64_against_reference_cuda_float64(softmax):
+    """Both implementations in double precision on the same inputs: 1e-10 (the orders of the
+    sums differ, nothing else)."""
+    w, _ = _inputs("cfg0_cpu_fp32", torch.float64)
+    f64 = torch.float64
+    t = dict(value=dev(w.value, f64), loc=dev(w.sampling_locations, f64),
+             attn=dev(w.attention_logits if softmax else w.attention_weights, f64),
+             grad_out=dev(w.grad_output, f64), shapes=dev(w.spatial_shapes),
+             starts=dev(w.level_start_index))
+    args = (t["value"], t["shapes"], t["starts"], t["loc"], t["attn"])
+    out = abi_forward(*args, softmax=softmax)
+    gv, gl, ga = abi_backward(*args, t["grad_out"], softmax=softmax)
+    r_out = ref_cuda.forward(*args, softmax=softmax)
+    r_gv, r_gl, r_ga = ref_cuda.backward(*args, t["grad_out"], softmax=softmax)
+    np64 = lambda x: x.detach().cpu().numpy().astype(np.float64)  # noqa: E731
+    for mine, theirs in ((out, r_out), (gv, r_gv), (gl, r_gl), (ga, r_ga)):
+        assert theirs.dtype == f64 or theirs.dtype == torch.float32
+        assert rel_err(np64(mine), np64(theirs)) <= 1e-10
