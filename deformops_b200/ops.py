@@ -67,7 +67,8 @@ _FORWARD_INPUTS = 9
 
 
 class _LaunchCounter:
-    """Counts kernel launches issued through this module (forward 1, backward 1 + memset)."""
+    """Counts launches issued through this module: forward 1 kernel; backward 3 kernels
+    (prepare, backward, finalize) with the replica scratch, else 1 kernel and 1 memset."""
 
     def __init__(self) -> None:
         self.kernels = 0
