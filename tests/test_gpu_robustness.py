@@ -1,0 +1,129 @@
+"""GPU checks modelled on the reference's robustness tests: bias of the 16-bit ``grad_value``
+sums, ``-inf`` logits, odd batch sizes, concurrent streams and host threads."""
+
+from __future__ import annotations
+
+import threading
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import msda_oracle as orc
+from tests._abi import abi_backward, abi_forward, dev, to_np
+from tests._golden import rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(seed, B, Q, G, D, K, levels, spread=1.2):
+    g = torch.Generator().manual_seed(seed)
+    shapes = torch.tensor(levels, dtype=torch.int64)
+    sizes = shapes[:, 0] * shapes[:, 1]
+    starts = torch.cumsum(sizes, 0) - sizes
+    S, L = int(sizes.sum()), len(levels)
+    value = torch.randn(B, S, G, D, generator=g)
+    loc = (torch.rand(B, Q, G, L, K, 2, generator=g) - 0.5) * spread + 0.5
+    logits = torch.randn(B, Q, G, L * K, generator=g)
+    grad_out = torch.randn(B, Q, G * D, generator=g)
+    return value, shapes, starts, loc, logits, grad_out
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_16bit_grad_value_has_no_directional_bias(dtype):
+    """The rounding error of the 16-bit sums must not lean along the true gradient (it would
+    act as a learning-rate change): |cos(mean error, truth)| < 0.05 over four runs, the
+    reference's criterion and shape (``tests/deformops/test_msda_bias.py:78-109``: Q=1024,
+    levels 48/24/12)."""
+    value, shapes, starts, loc, logits, grad_out = _case(
+        7, 2, 1024, 8, 32, 4, [(48, 48), (24, 24), (12, 12)], spread=1.0)
+    attn = logits.softmax(-1)
+    v, a, go = dev(value, dtype), dev(attn, dtype), dev(grad_out, dtype)
+    l, sh, st = dev(loc, torch.float32), dev(shapes), dev(starts)
+    truth, _, _ = orc.backward(v.cpu(), shapes, starts, l.cpu(), a.cpu(), go.cpu(), precision="f64")
+    runs = [to_np(abi_backward(v, sh, st, l, a, go)[0]) for _ in range(4)]
+    mean_err = (np.mean(runs, axis=0) - truth).ravel()
+    t = np.asarray(truth).ravel()
+    cos = float(mean_err @ t / (np.linalg.norm(mean_err) * np.linalg.norm(t) + 1e-30))
+    assert abs(cos) < 0.05, cos
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_softmax_with_minus_infinity_logits_and_wide_locations(dtype):
+    """A masked-out point (``-inf`` logit) gets probability zero, nothing becomes NaN, and
+    locations far outside the image only drop out (reference:
+    ``tests/deformops/test_msda_softmax_before_softmax_gpu.py:79-126``)."""
+    value, shapes, starts, loc, logits, grad_out = _case(
+        3, 2, 60, 4, 32, 4, [(9, 11), (5, 6), (3, 3)], spread=4.0)
+    logits[:, ::3, :, 5] = float("-inf")
+    logits[0, 1, 0, :-1] = float("-inf")          # a pair with a single live point
+    v, a, go = dev(value, dtype), dev(logits, dtype), dev(grad_out, dtype)
+    l, sh, st = dev(loc, torch.float32), dev(shapes), dev(starts)
+    out = abi_forward(v, sh, st, l, a, softmax=True)
+    gv, gl, ga = abi_backward(v, sh, st, l, a, go, softmax=True)
+    for t in (out, gv, gl, ga):
+        assert torch.isfinite(t).all()
+    args = (v.cpu(), shapes, starts, l.cpu(), a.cpu())
+    e_out = orc.forward(*args, softmax=True, precision="f64")
+    e_gv, e_gl, e_ga = orc.backward(*args, go.cpu(), softmax=True, precision="f64")
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    assert rel_err(to_np(out), e_out) <= tol
+    assert rel_err(to_np(gv), e_gv) <= tol
+    assert rel_err(to_np(ga), e_ga) <= tol
+    assert (to_np(ga)[:, ::3, :, 5] == 0).all()    # no gradient into a masked logit
+
+
+@pytest.mark.parametrize("batch", [7, 70, 96])
+def test_odd_batch_sizes(batch):
+    """Batches that do not divide any internal tile (the reference splits them at
+    ``chunk_step``, ``tests/deformops/test_release_hardening.py:280-301``; here one launch)."""
+    value, shapes, starts, loc, logits, grad_out = _case(
+        batch, batch, 13, 2, 16, 4, [(6, 7), (3, 4)])
+    attn = logits.softmax(-1)
+    v, a, go = (dev(x, torch.float32) for x in (value, attn, grad_out))
+    l, sh, st = dev(loc, torch.float32), dev(shapes), dev(starts)
+    out = abi_forward(v, sh, st, l, a)
+    gv, gl, ga = abi_backward(v, sh, st, l, a, go)
+    args = (value, shapes, starts, loc, attn)
+    assert rel_err(to_np(out), orc.forward(*args, precision="f64")) <= 1e-5
+    e_gv, e_gl, e_ga = orc.backward(*args, grad_out, precision="f64")
+    assert rel_err(to_np(gv), e_gv) <= 1e-4 and rel_err(to_np(ga), e_ga) <= 1e-4
+
+
+def test_concurrent_streams_and_host_threads():
+    """Calls from several host threads on their own streams (the autograd engine calls the
+    backward from another thread): every result equals the single-threaded one."""
+    from deformops_b200.registry import msda
+
+    value, shapes, starts, loc, logits, grad_out = _case(
+        11, 2, 500, 8, 32, 4, [(20, 20), (10, 10), (5, 5)])
+    v, a, go = (dev(x, torch.float32) for x in (value, logits, grad_out))
+    l, sh, st = dev(loc, torch.float32), dev(shapes), dev(starts)
+
+    def step():
+        vv, ll, aa = (t.detach().clone().requires_grad_() for t in (v, l, a))
+        out = msda(vv, sh, st, ll, aa, softmax=True)
+        grads = torch.autograd.grad(out, [vv, ll, aa], go)
+        return out, grads
+
+    want_out, want = step()
+    torch.cuda.synchronize()
+    results, errors = {}, []
+
+    def worker(i):
+        try:
+            with torch.cuda.stream(torch.cuda.Stream()):
+                for _ in range(5):
+                    results[i] = step()
+                torch.cuda.current_stream().synchronize()
+        except Exception as exc:  # noqa: BLE001 - reported through the assertion below
+            errors.append(exc)
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(4)]
+    [t.start() for t in threads]
+    [t.join() for t in threads]
+    assert not errors, errors
+    for out, grads in results.values():
+        assert torch.equal(out, want_out)
+        assert torch.equal(grads[1], want[1]) and torch.equal(grads[2], want[2])
+        assert rel_err(to_np(grads[0]), to_np(want[0])) <= 1e-6
