@@ -29,10 +29,10 @@
 #include "msda_common.cuh"
 
 // tuning knobs (compile-time): points in flight together and CTAs per SM the registers allow.
-// Measured on B200 at the headline shape (backward call, ms): unroll 1 / 4 CTAs 0.611,
-// 1 / 3 0.618, 2 / 3 0.633, 3 / 3 0.648, 2 / 4 0.688, 2 / 2 0.734, 1 / 5 0.833.
+// Measured on B200 at the headline shape (backward call, ms): unroll 2 / 4 CTAs 0.583,
+// 3 / 4 0.585, 1 / 4 0.593, 1 / 3 0.604, 2 / 3 0.605, 4 / 4 0.680, 1 / 5 0.815.
 #ifndef MSDA_BWD_UNROLL
-#define MSDA_BWD_UNROLL 1
+#define MSDA_BWD_UNROLL 2
 #endif
 #ifndef MSDA_BWD_MIN_CTAS
 #define MSDA_BWD_MIN_CTAS 4
@@ -87,8 +87,14 @@ __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const 
     T *grad_value = reinterpret_cast<T *>(p.grad_value);
     T *scratch = reinterpret_cast<T *>(p.scratch);
 
-    for (int64_t group = (int64_t)blockIdx.x * nwarps + warp; group < p.num_groups;
-         group += (int64_t)gridDim.x * nwarps) {
+    // A CTA walks `passes` ADJACENT sets of nwarps groups; the grid covers every group.  (A
+    // grid-stride loop here cost registers the kernel does not have: 0.617 ms per call with it
+    // against 0.583 ms in this form.  The register allocation at 64 registers is sensitive to
+    // the shape of this loop: check `-Xptxas -v` for spills after touching it.)
+    const int passes = p.passes > 1 ? p.passes : 1;
+    for (int pass = 0; pass < passes; ++pass) {
+        const int64_t group = ((int64_t)blockIdx.x * passes + pass) * nwarps + warp;
+        if (group >= p.num_groups) break;
         const int64_t pair0 = group * ppw;
         const int nlive = (int)min((int64_t)ppw, total_pairs - pair0);
         if constexpr (SOFTMAX) {
@@ -343,7 +349,22 @@ cudaError_t launch_typed(const Params &p, cudaStream_t stream) {
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    kernel<<<p.grid, p.threads, smem, stream>>>(p);
+    // Two adjacent passes per CTA once that still leaves every SM several waves of CTAs
+    // (the per-CTA prologue is paid half as often; worth about 0.2 % at the headline shape).
+    Params q = p;
+    int device = 0, sms = 0, per_sm = 0;
+    q.passes = 1;
+    if (cudaGetDevice(&device) == cudaSuccess &&
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) == cudaSuccess &&
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, p.threads, smem) ==
+            cudaSuccess &&
+        sms > 0 && per_sm > 0 && p.grid >= 8u * (unsigned)(sms * per_sm))
+        q.passes = 2;
+    const int64_t per_cta = (int64_t)(p.threads / 32) * q.passes;   // groups one CTA covers
+    const int64_t ctas = (p.num_groups + per_cta - 1) / per_cta;
+    if (ctas > 0x7fffffffll) return cudaErrorInvalidConfiguration;   // > 10^11 pairs
+    q.grid = (unsigned)ctas;
+    kernel<<<q.grid, q.threads, smem, stream>>>(q);
     return cudaGetLastError();
 }
 

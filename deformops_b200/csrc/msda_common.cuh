@@ -55,6 +55,7 @@ struct Params {
     int64_t num_groups;     // ceil(B*Q*G / pairs per warp)
     unsigned grid;
     int region_window_ints; // region-tiled backward: int32 window accumulators per CTA (0: none)
+    int passes;             // backward: adjacent sets of groups one CTA walks (0 or 1: one)
     // Fused location arithmetic.  When `ref` is set, `loc` / `grad_loc` hold the predicted
     // offsets (B,Q,G,L,K,2) and their gradient, and a point samples at
     //   ref_coords == 2:  ref.xy + offset / (W_l, H_l)
