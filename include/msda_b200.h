@@ -177,9 +177,12 @@ int msda_b200_backward_static_scratch(const void *value, const int64_t *spatial_
                                       int device, void *stream);
 
 /*
- * Launch geometry the library would use for a shape, for harnesses that count launches
- * or size grids: number of CTAs, threads per CTA and dynamic shared memory of the forward
- * (*_fwd) and backward (*_bwd) kernels.  Pure function of its arguments.
+ * Launch geometry the library plans for a shape, for harnesses that count launches or size
+ * grids: `grid` = CTAs needed to give every group of (query, head) pairs one warp pass,
+ * threads per CTA and dynamic shared memory of the forward (*_fwd) and backward (*_bwd)
+ * kernels.  Pure function of its arguments and independent of the device; at launch time the
+ * forward caps its grid at the number of CTAs the device holds at once (persistent CTAs) and
+ * the backward lets a CTA make two adjacent passes when that still leaves several waves.
  * Replaces: forward_thread_layout / backward_thread_layout
  *   sources/deformops/core/tuning.py:55-133, include/msda_launch.cuh:26-52
  */
