@@ -14,7 +14,8 @@ import pathlib
 import shutil
 import subprocess
 
-__all__ = ["LIB_PATH", "SOURCES", "build_library", "is_stale"]
+__all__ = ["LIB_PATH", "SOURCES", "TORCH_BINDING_PATH", "build_library", "build_torch_binding",
+           "is_stale"]
 
 PKG = pathlib.Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
@@ -23,6 +24,8 @@ LIB_PATH = LIB_DIR / "libmsda_b200.so"
 SOURCES = ["msda_forward.cu", "msda_backward.cu", "msda_abi.cu", "msda_static_scratch.cu",
            "msda_l2_window.cu", "msda_backward_region.cu", "msda_f64.cu"]
 HEADERS = [CSRC / "msda_common.cuh", PKG.parent / "include" / "msda_b200.h"]
+#: native dispatcher registration for Python-free processes (see csrc/torch_binding.cpp)
+TORCH_BINDING_PATH = LIB_DIR / "libmsda_b200_torch.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -84,7 +87,40 @@ def build_library(force: bool = False, verbose: bool = False) -> pathlib.Path:
     return LIB_PATH
 
 
+def build_torch_binding(force: bool = False) -> pathlib.Path:
+    """Compile ``csrc/torch_binding.cpp`` against the installed torch into
+    ``_lib/libmsda_b200_torch.so`` (links ``libmsda_b200.so`` next to it).  Needs a host C++
+    compiler and the torch headers; the Python package itself never loads the result."""
+    src = CSRC / "torch_binding.cpp"
+    build_library()
+    if (not force and TORCH_BINDING_PATH.exists()
+            and TORCH_BINDING_PATH.stat().st_mtime > max(src.stat().st_mtime,
+                                                         LIB_PATH.stat().st_mtime)):
+        return TORCH_BINDING_PATH
+    import torch
+    from torch.utils import cpp_extension
+
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if cxx is None:
+        raise RuntimeError("no host C++ compiler found: cannot build the torch binding")
+    torch_lib = pathlib.Path(torch.__file__).parent / "lib"
+    tmp = TORCH_BINDING_PATH.with_suffix(".so.tmp")
+    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", str(src),
+           *[f"-I{p}" for p in cpp_extension.include_paths("cuda")],
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           "-o", str(tmp), f"-L{torch_lib}", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10",
+           "-lc10_cuda", f"-L{LIB_DIR}", "-lmsda_b200", "-Wl,-rpath,$ORIGIN",
+           f"-Wl,-rpath,{torch_lib}"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"building the torch binding failed:\n{res.stderr[-4000:]}")
+    os.replace(tmp, TORCH_BINDING_PATH)
+    return TORCH_BINDING_PATH
+
+
 if __name__ == "__main__":
     import sys
 
     print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--torch-binding" in sys.argv:
+        print(build_torch_binding(force="--force" in sys.argv))

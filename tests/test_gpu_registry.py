@@ -251,24 +251,30 @@ def test_export_and_dynamo_record_the_public_op():
     assert torch.equal(compiled(*fewer), Layer()(*fewer))
 
 
-def test_aot_inductor_package_runs_in_a_fresh_process(tmp_path):
-    """An AOTInductor package of a module that calls the operator runs in a new process once
-    that process has imported the package (which registers the ops and their CUDA
-    implementations) - the recipe the reference documents for its CUDA operators
-    (``docs/export.md``: "needs their library loaded first").  Export + compile happen in one
-    child process, loading and running in another."""
+def test_aot_inductor_package_in_fresh_processes_with_and_without_python_registration(tmp_path):
+    """An AOTInductor package of a module that calls the operator is compiled in one child
+    process and run in two others.  The first imports ``deformops_b200`` (which registers the
+    ops and their CUDA implementations over ctypes) - the recipe the reference documents for
+    its CUDA operators (``docs/export.md``: "needs their library loaded first").  The second
+    never imports the package: it loads ``libmsda_b200_torch.so`` (csrc/torch_binding.cpp),
+    which registers the private operators with the dispatcher natively, runs the same package
+    and calls the backward operator directly; results equal the Python-registered ones."""
     import os
     import shutil
     import subprocess
     import sys
 
-    c = load("small_b")
+    from deformops_b200._build import TORCH_BINDING_PATH, build_torch_binding
+
+    if not TORCH_BINDING_PATH.exists():
+        build_torch_binding()
+    c, t = _case("small_b")
+    K = t["loc"].shape[4]
     torch.save({k: torch.as_tensor(c[k]) for k in ("value", "spatial_shapes", "level_start_index",
-                                                   "loc", "attn_logits")}, tmp_path / "in.pt")
+                                                   "loc", "attn_logits", "grad_out")},
+               tmp_path / "in.pt")
     root = pathlib.Path(__file__).resolve().parents[1]
     env = dict(os.environ)
-    # Inductor compiles its wrapper with $CXX; use the system compiler found on PATH (an
-    # environment may point CXX at a toolchain without OpenMP support files)
     if shutil.which("g++"):
         env["CXX"] = shutil.which("g++")
     compile_script = f"""
@@ -279,13 +285,29 @@ args = tuple(c[k].cuda() for k in ("value", "spatial_shapes", "level_start_index
 class Layer(torch.nn.Module):
     def forward(self, value, shapes, starts, loc, attn):
         return msda(value, shapes, starts, loc, attn, method="softmax") * 2.0
-expected = Layer()(*args)
+torch.save(Layer()(*args).cpu(), r'{tmp_path / 'expected.pt'}')
 exported = torch.export.export(Layer(), args)
 torch._inductor.aoti_compile_and_package(exported, package_path=r'{tmp_path / 'layer.pt2'}')
-torch.save(expected.cpu(), r'{tmp_path / 'expected.pt'}')
 print('compiled')
 """
-    run_script = f"""
+    native_script = f"""
+import sys, torch
+torch.ops.load_library(r'{TORCH_BINDING_PATH}')
+c = torch.load(r'{tmp_path / 'in.pt'}')
+args = tuple(c[k].cuda() for k in ("value", "spatial_shapes", "level_start_index", "loc", "attn_logits"))
+runner = torch._inductor.aoti_load_package(r'{tmp_path / 'layer.pt2'}')
+out = runner(*args)
+torch.cuda.synchronize()
+assert torch.equal(out.cpu(), torch.load(r'{tmp_path / 'expected.pt'}'))
+grads = torch.ops.deformops_b200.msda_softmax_backward(*args, c["grad_out"].cuda(), 128, {K}, 0, 0)
+torch.save([g.cpu() for g in grads], r'{tmp_path / 'native_grads.pt'}')
+assert 'deformops_b200' not in sys.modules
+print('native-ok')
+"""
+    done = subprocess.run([sys.executable, "-c", compile_script], cwd=root, env=env,
+                          capture_output=True, text=True, timeout=900)
+    assert done.returncode == 0 and "compiled" in done.stdout, done.stderr[-3000:]
+    python_script = f"""
 import torch
 import deformops_b200
 from deformops_b200._loader import loaded
@@ -294,12 +316,19 @@ args = tuple(c[k].cuda() for k in ("value", "spatial_shapes", "level_start_index
 runner = torch._inductor.aoti_load_package(r'{tmp_path / 'layer.pt2'}')
 out = runner(*args)
 torch.cuda.synchronize()
-expected = torch.load(r'{tmp_path / 'expected.pt'}')
-assert torch.equal(out.cpu(), expected), (out.cpu() - expected).abs().max()
+assert torch.equal(out.cpu(), torch.load(r'{tmp_path / 'expected.pt'}'))
 assert loaded()
-print('aoti-ok')
+print('python-ok')
 """
-    for script, marker in ((compile_script, "compiled"), (run_script, "aoti-ok")):
-        done = subprocess.run([sys.executable, "-c", script], cwd=root, env=env,
-                              capture_output=True, text=True, timeout=900)
-        assert done.returncode == 0 and marker in done.stdout, done.stderr[-3000:]
+    done = subprocess.run([sys.executable, "-c", python_script], cwd=root, env=env,
+                          capture_output=True, text=True, timeout=900)
+    assert done.returncode == 0 and "python-ok" in done.stdout, done.stderr[-3000:]
+    done = subprocess.run([sys.executable, "-c", native_script], cwd=tmp_path, env=env,
+                          capture_output=True, text=True, timeout=900)
+    assert done.returncode == 0 and "native-ok" in done.stdout, done.stderr[-3000:]
+    native = torch.load(tmp_path / "native_grads.pt")
+    mine = torch.ops.deformops_b200.msda_softmax_backward(
+        t["value"], t["shapes"], t["starts"], t["loc"], t["attn_logits"], t["grad_out"], 128, K,
+        0, 0)
+    assert torch.equal(native[1], mine[1].cpu()) and torch.equal(native[2], mine[2].cpu())
+    torch.testing.assert_close(native[0], mine[0].cpu(), rtol=1e-6, atol=1e-6)
