@@ -76,3 +76,30 @@ def test_c_program_calls_the_library(tmp_path):
     assert done.returncode == 0, done.stderr
     run = subprocess.run([str(exe), str(LIB_PATH)], capture_output=True, text=True)
     assert run.returncode == 0 and "ok" in run.stdout, (run.returncode, run.stderr)
+
+
+def test_native_torch_binding_defines_the_same_schemas(tmp_path):
+    """``libmsda_b200_torch.so`` loaded into a process that never imports the package defines
+    the four private operators with exactly the schemas ``ops.py`` defines."""
+    import subprocess
+    import sys
+
+    if shutil.which("g++") is None:
+        pytest.skip("g++ not installed")
+    from deformops_b200._build import build_torch_binding
+    from deformops_b200.ops import _BACKWARD_SCHEMA, _FORWARD_SCHEMA, PRIVATE_OPS
+
+    binding = build_torch_binding()
+    script = (
+        "import sys, torch\n"
+        f"torch.ops.load_library(r'{binding}')\n"
+        f"for name in {PRIVATE_OPS!r}:\n"
+        "    print(name, '|', str(getattr(torch.ops.deformops_b200, name).default._schema))\n"
+        "assert 'deformops_b200' not in sys.modules\n")
+    done = subprocess.run([sys.executable, "-c", script], cwd=tmp_path, capture_output=True,
+                          text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    seen = dict(line.split(" | ") for line in done.stdout.strip().splitlines())
+    for name in PRIVATE_OPS:
+        want = _FORWARD_SCHEMA if name.endswith("forward") else _BACKWARD_SCHEMA
+        assert seen[name] == f"deformops_b200::{name}{want}", (seen[name], want)
