@@ -186,6 +186,8 @@ def test_full_size_adjoint_identities():
     (1, 5, 24, [(7, 7), (4, 4)], 2, 11),           # D not a power of two
     (3, 16, 16, [(4, 4), (2, 2), (1, 1)], 8, 65),
     (1, 4, 64, [(3, 3)] * 5, 4, 9),
+    (1, 2, 256, [(5, 4), (2, 3)], 2, 7),           # float32: 64 vectors, two channel passes per lane
+    (2, 1, 512, [(4, 4)], 3, 5),                   # 16-bit: 64 vectors as well
 ])
 def test_shape_envelope(shape, dtype):
     B, G, D, levels, K, Q = shape
