@@ -197,3 +197,22 @@ def test_functional_argument_errors():
         msda_from_offsets(v, sh, st, r[:, :5], off, a)
     out = msda_from_offsets(v, sh, st, r[:, :0], off[:, :0], a[:, :0])
     assert out.shape == (1, 0, v.shape[2] * v.shape[3])
+
+
+@pytest.mark.parametrize("coords", [2, 4])
+def test_fused_offsets_with_odd_points_heads_and_ragged_levels(coords):
+    """K = 3 (``offset / K`` is not a power-of-two scale), 3 heads, levels down to 1 x 2."""
+    value, shapes, starts, ref, offsets, attn, grad_out = _case(
+        31, coords, B=3, Q=41, G=3, D=8, K=3, levels=[(7, 5), (3, 4), (1, 2)])
+    v, a, go = (dev(x, torch.float32) for x in (value, attn, grad_out))
+    off, r, sh, st = dev(offsets, torch.float32), dev(ref, torch.float32), dev(shapes), dev(starts)
+    out = abi_forward_offsets(v, sh, st, r, off, a, softmax=True)
+    gv, goff, ga = abi_backward_offsets(v, sh, st, r, off, a, go, softmax=True)
+    loc, dloc = _torch_locations(ref, torch.as_tensor(offsets), shapes)
+    args = (value, shapes, starts, loc, attn)
+    e_out = orc.forward(*args, softmax=True, precision="f64")
+    e_gv, e_gl, e_ga = orc.backward(*args, grad_out, softmax=True, precision="f64")
+    keep = _stable_points(to_np(loc), shapes)[..., None]
+    assert rel_err(to_np(out), e_out) <= 1e-5
+    assert rel_err(to_np(gv), e_gv) <= 1e-4 and rel_err(to_np(ga), e_ga) <= 1e-4
+    assert rel_err(to_np(goff) * keep, np.asarray(e_gl) * dloc.numpy() * keep) <= 1e-4
