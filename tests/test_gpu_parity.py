@@ -114,8 +114,13 @@ def test_fp32_matches_reference_fixtures(name, method):
 @pytest.mark.parametrize("name", ["small_b", "small_c", "k8_d64", "ragged"])
 def test_16bit_matches_oracle_on_fixture_inputs(name, dtype, method):
     c = load(name)
+    # Small fixtures: a handful of elements decide the max-norm metric and the order of the
+    # 16-bit additions changes from run to run (measured over 30 runs: grad_value up to 7.4e-3,
+    # typically 5e-3..7e-3), so the gradients get the reference's own 16-bit tolerance of 2e-2
+    # (tests/deformops/test_experimental_parity.py:58); the full-size configurations below,
+    # whose error barely moves between runs, keep 1e-2.
     run_case(name, c["value"], c["spatial_shapes"], c["level_start_index"], c["loc"],
-             attn_for(c, method), c["grad_out"], dtype, method)
+             attn_for(c, method), c["grad_out"], dtype, method, tol=(1e-2, 2e-2))
 
 
 @pytest.mark.parametrize("method", METHODS)
