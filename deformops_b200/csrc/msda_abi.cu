@@ -262,6 +262,16 @@ int forward_impl(const void *value, const int64_t *spatial_shapes, const int64_t
     const int st = plan(p, B, S, G, D, Q, L, K, dtype, apply_softmax != 0);
     if (st != MSDA_B200_OK) return st;
     if (B == 0 || Q == 0) return MSDA_B200_OK;
+    if (S == 0) {
+        // nothing to sample from: every point falls outside, the output is zero
+        if (!out) return fail(MSDA_B200_INVALID_ARGUMENT, "forward: null pointer argument");
+        DeviceGuard guard(device);
+        if (guard.err != cudaSuccess) return cuda_fail(guard.err, "forward: selecting the device");
+        const cudaError_t e =
+            cudaMemsetAsync(out, 0, (size_t)(B * Q * G * D) * element_size(dtype),
+                            static_cast<cudaStream_t>(stream));
+        return e == cudaSuccess ? MSDA_B200_OK : cuda_fail(e, "forward: clearing the output");
+    }
     if (!value || !spatial_shapes || !level_start_index || !loc || !attn || !out)
         return fail(MSDA_B200_INVALID_ARGUMENT, "forward: null pointer argument");
     if (!aligned16(value) || !aligned16(loc) || !aligned16(attn) || !aligned16(out))
@@ -300,6 +310,20 @@ int backward_impl(const void *value, const int64_t *spatial_shapes,
     if (st != MSDA_B200_OK) return st;
     if (B == 0) return MSDA_B200_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (S == 0) {
+        // an empty value tensor: no point samples anything, all gradients are zero
+        if (Q == 0) return MSDA_B200_OK;
+        if (!pts.grad || !grad_attn)
+            return fail(MSDA_B200_INVALID_ARGUMENT, "backward: null pointer argument");
+        DeviceGuard guard(device);
+        if (guard.err != cudaSuccess) return cuda_fail(guard.err, "backward: selecting the device");
+        const size_t points = (size_t)(B * Q * G) * (size_t)(L * K);
+        const size_t loc_elem =
+            pts.ref != nullptr && pts.offsets16 ? 2 : (dtype == MSDA_B200_F64 ? 8 : 4);
+        cudaError_t e = cudaMemsetAsync(pts.grad, 0, points * 2 * loc_elem, s);
+        if (e == cudaSuccess) e = cudaMemsetAsync(grad_attn, 0, points * element_size(dtype), s);
+        return e == cudaSuccess ? MSDA_B200_OK : cuda_fail(e, "backward: clearing the gradients");
+    }
     const bool use_scratch = scratch != nullptr &&
                              (dtype == MSDA_B200_F16 || dtype == MSDA_B200_BF16) && S > 0 && Q > 0;
     if (use_scratch) {

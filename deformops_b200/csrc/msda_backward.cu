@@ -266,7 +266,7 @@ __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const 
 __device__ __forceinline__ int level_of(const LevelTable &lt, int L, int s) {
     int l = 0;
     for (int i = 1; i < L; ++i)
-        if (s >= lt.start[i]) l = i;
+        if (lt.H[i] > 0 && s >= lt.start[i]) l = i;   // empty levels own no position
     return l;
 }
 
@@ -321,6 +321,11 @@ __global__ void __launch_bounds__(256) finalize_kernel(const Params p) {
         const int l = level_of(lt, p.L, s);
         const int reps = lt.rep[l];
         if (reps == 0) continue;
+        if (s < lt.start[l] || s - lt.start[l] >= lt.H[l] * lt.W[l]) {
+            // a position outside every level (gap in a malformed table): nothing was added
+            reinterpret_cast<uint4 *>(p.grad_value)[v] = make_uint4(0u, 0u, 0u, 0u);
+            continue;
+        }
         const int64_t b = row / p.S;
         const T *src = reinterpret_cast<const T *>(p.scratch) + b * (int64_t)lt.scratch_sample_elems +
                        lt.rep_base[l] + (int64_t)(s - lt.start[l]) * GD + (v - row * vec_per_row) * V;

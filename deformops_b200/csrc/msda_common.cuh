@@ -286,7 +286,9 @@ __device__ inline void plan_replicas(LevelTable &t, const Params &p) {
         for (int l = 0; l < p.L; ++l) {
             const long long hw = (long long)t.H[l] * t.W[l];
             // R = ceil(n / adds) replicas; n <= adds: the one accumulator is grad_value itself
-            const long long r = n4 > adds * hw ? (n4 + adds * hw - 1) / (adds * hw) : 0;
+            // (an empty level, hw == 0, receives nothing and gets no replicas)
+            const long long r =
+                hw > 0 && n4 > adds * hw ? (n4 + adds * hw - 1) / (adds * hw) : 0;
             t.rep[l] = (int)r;
             total += r * hw * GD;
         }
@@ -304,13 +306,21 @@ __device__ inline void plan_replicas(LevelTable &t, const Params &p) {
     for (int l = 0; l < p.L; ++l) t.rep[l] = 0;   // cannot happen for sane tables: all direct
 }
 
+// Loads the level table from device memory.  A level that does not lie inside the value tensor
+// (non-positive size, negative start, or start + H*W beyond S) becomes an empty level at
+// position 0: every point on it is skipped, so a malformed table produces zeros for that level
+// instead of an access outside `value` / `grad_value`.
 __device__ __forceinline__ void load_level_table(LevelTable &t, const Params &p) {
     if (threadIdx.x < p.L) {
-        const int H = (int)p.spatial_shapes[2 * threadIdx.x];
-        const int W = (int)p.spatial_shapes[2 * threadIdx.x + 1];
+        const int64_t h = p.spatial_shapes[2 * threadIdx.x];
+        const int64_t w = p.spatial_shapes[2 * threadIdx.x + 1];
+        const int64_t first = p.level_start_index[threadIdx.x];
+        const bool fits = h > 0 && w > 0 && first >= 0 && h <= p.S && w <= p.S &&
+                          h * w <= p.S && first <= p.S - h * w;
+        const int H = fits ? (int)h : 0, W = fits ? (int)w : 0;
         t.H[threadIdx.x] = H;
         t.W[threadIdx.x] = W;
-        t.start[threadIdx.x] = (int)p.level_start_index[threadIdx.x];
+        t.start[threadIdx.x] = fits ? (int)first : 0;
         t.rowstride[threadIdx.x] = W * p.G * p.D;
         t.level_elems[threadIdx.x] = (unsigned)H * (unsigned)W * (unsigned)(p.G * p.D);
     }
@@ -343,7 +353,8 @@ __device__ __forceinline__ PointGeom locate(float x, float y, int H, int W, int 
     g.Wf = (float)W;
     const float px = fmaf(x, g.Wf, -0.5f);
     const float py = fmaf(y, g.Hf, -0.5f);
-    const bool inside = (py >= -1.f) && (px >= -1.f) && (py < g.Hf) && (px < g.Wf);
+    // (an empty level, H == 0, skips everything: see load_level_table)
+    const bool inside = (py >= -1.f) && (px >= -1.f) && (py < g.Hf) && (px < g.Wf) && H > 0;
     // keep the arithmetic finite for skipped points (their loads are predicated off)
     const float sx = inside ? px : 0.f;
     const float sy = inside ? py : 0.f;

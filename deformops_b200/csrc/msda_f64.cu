@@ -21,11 +21,17 @@ struct Levels64 {
     int H[kMaxLevels], W[kMaxLevels], start[kMaxLevels];
 };
 
+// a level that does not lie inside the value tensor becomes an empty level (all points skipped)
 __device__ __forceinline__ void load_levels(Levels64 &t, const Params &p) {
     if (threadIdx.x < p.L) {
-        t.H[threadIdx.x] = (int)p.spatial_shapes[2 * threadIdx.x];
-        t.W[threadIdx.x] = (int)p.spatial_shapes[2 * threadIdx.x + 1];
-        t.start[threadIdx.x] = (int)p.level_start_index[threadIdx.x];
+        const int64_t h = p.spatial_shapes[2 * threadIdx.x];
+        const int64_t w = p.spatial_shapes[2 * threadIdx.x + 1];
+        const int64_t first = p.level_start_index[threadIdx.x];
+        const bool fits = h > 0 && w > 0 && first >= 0 && h <= p.S && w <= p.S &&
+                          h * w <= p.S && first <= p.S - h * w;
+        t.H[threadIdx.x] = fits ? (int)h : 0;
+        t.W[threadIdx.x] = fits ? (int)w : 0;
+        t.start[threadIdx.x] = fits ? (int)first : 0;
     }
     __syncthreads();
 }
@@ -40,7 +46,7 @@ struct Point64 {
 __device__ __forceinline__ Point64 locate64(double x, double y, int H, int W, int start, int GD) {
     Point64 g;
     const double px = x * (double)W - 0.5, py = y * (double)H - 0.5;
-    g.inside = (py >= -1.0) && (px >= -1.0) && (py < (double)H) && (px < (double)W);
+    g.inside = (py >= -1.0) && (px >= -1.0) && (py < (double)H) && (px < (double)W) && H > 0;
     const double sx = g.inside ? px : 0.0, sy = g.inside ? py : 0.0;
     const double r0f = floor(sy), c0f = floor(sx);
     const int r0 = (int)r0f, c0 = (int)c0f;

@@ -106,8 +106,9 @@ __global__ void __launch_bounds__(256, MSDA_FWD_MIN_CTAS) forward_kernel(const P
                     // pixel inside it, so the gather needs no predicates; a skipped point
                     // (geo.r0 = geo.c0 = 0, all weights 0) reads pixel (0, 0) of its level.
                     const int H = lt.H[l], W = lt.W[l];
-                    const int ra = max(geo.r0, 0), rb = min(geo.r0 + 1, H - 1);
-                    const int ca = max(geo.c0, 0), cb = min(geo.c0 + 1, W - 1);
+                    // (an empty level has H = W = 0 and start 0: everything lands on pixel 0)
+                    const int ra = max(geo.r0, 0), rb = max(min(geo.r0 + 1, H - 1), 0);
+                    const int ca = max(geo.c0, 0), cb = max(min(geo.c0 + 1, W - 1), 0);
                     const int row_a = (lt.start[l] + ra * W) * GD, row_b = (lt.start[l] + rb * W) * GD;
                     A = make_uint4((unsigned)(row_a + ca * GD), (unsigned)(row_a + cb * GD),
                                    (unsigned)(row_b + ca * GD), (unsigned)(row_b + cb * GD));

@@ -14,7 +14,10 @@
  *       loc / grad_loc       (B, Q, G, L, K, 2)    float32, (x, y) normalised to [0, 1]
  *       attn / grad_attn     (B, Q, G, L*K)        element type `dtype`
  *       out / grad_out       (B, Q, G*D)           element type `dtype`
- *   - The level tables are read on the device; no call synchronises with the host.
+ *   - The level tables are read on the device; no call synchronises with the host.  A level
+ *     whose table entry does not lie inside the value tensor (non-positive height or width,
+ *     negative start, start + height*width > S) is treated as empty: its points contribute
+ *     nothing and receive zero gradients; no address outside the tensors is formed.
  *   - Work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = default
  *     stream) and the call returns immediately.  Inputs are borrowed, outputs are
  *     caller-allocated; nothing is allocated or freed here.

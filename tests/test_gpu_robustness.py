@@ -127,3 +127,63 @@ def test_concurrent_streams_and_host_threads():
         assert torch.equal(out, want_out)
         assert torch.equal(grads[1], want[1]) and torch.equal(grads[2], want[2])
         assert rel_err(to_np(grads[0]), to_np(want[0])) <= 1e-6
+
+
+def test_malformed_level_tables_are_skipped_not_dereferenced():
+    """Levels that do not lie inside the value tensor (too large, negative start, zero size,
+    running past the end) act as empty levels: their points contribute nothing and get zero
+    gradients.  The buffers here are allocated far larger than the size handed to the library,
+    so the addresses such a table describes are inside the allocation either way; the test
+    reads the behaviour off the results."""
+    import ctypes
+
+    from deformops_b200._loader import load_library
+
+    shim = load_library()
+    G, D, K, Q, S, rows = 2, 8, 2, 9, 16, 256
+    g = torch.Generator().manual_seed(5)
+    shapes = torch.tensor([[8, 8], [2, 4], [0, 5], [3, 3], [3, 3]], dtype=torch.int64)
+    starts = torch.tensor([0, 4, 1, -4, 14], dtype=torch.int64)       # only level 1 fits S = 16
+    L = shapes.shape[0]
+    value = torch.randn(1, rows, G, D, generator=g)
+    loc = torch.rand(1, Q, G, L, K, 2, generator=g)
+    attn = torch.rand(1, Q, G, L * K, generator=g)
+    grad_out = torch.randn(1, Q, G * D, generator=g)
+    v, l, a, go = (dev(t, torch.float32) for t in (value, loc, attn, grad_out))
+    sh, st = dev(shapes), dev(starts)
+    out = torch.full((1, Q, G * D), float("nan"), device="cuda")
+    gv = torch.full((1, rows, G, D), float("nan"), device="cuda")
+    gl, ga = torch.full_like(l, float("nan")), torch.full_like(a, float("nan"))
+    p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    z = ctypes.c_void_p(0)
+    assert shim.forward(p(v), p(sh), p(st), p(l), p(a), p(out), 1, S, G, D, Q, L, K, 0, 0, 0, z) == 0
+    assert shim.backward(p(v), p(sh), p(st), p(l), p(a), p(go), p(gv), p(gl), p(ga), None, 0, 0,
+                         1, S, G, D, Q, L, K, 0, 0, 1, 0, z) == 0
+    torch.cuda.synchronize()
+    # expectation: the one valid level alone, on a consistent table
+    one = (value[:, :S], shapes[1:2], starts[1:2], loc[:, :, :, 1:2].contiguous(),
+           attn.view(1, Q, G, L, K)[:, :, :, 1].contiguous())
+    e_out = orc.forward(*one, precision="f64")
+    e_gv, e_gl, e_ga = orc.backward(*one, grad_out, precision="f64")
+    assert rel_err(to_np(out), e_out) <= 1e-5
+    assert rel_err(to_np(gv[:, :S]), e_gv) <= 1e-4
+    assert torch.isnan(gv[:, S:]).all()                       # nothing beyond S rows was touched
+    gl5, ga5 = gl.cpu(), ga.cpu().view(1, Q, G, L, K)
+    assert rel_err(gl5[:, :, :, 1:2].numpy().astype(np.float64), e_gl) <= 1e-4
+    assert rel_err(ga5[:, :, :, 1].numpy().astype(np.float64), e_ga) <= 1e-4
+    for bad in (0, 2, 3, 4):
+        assert (gl5[:, :, :, bad] == 0).all() and (ga5[:, :, :, bad] == 0).all()
+
+
+def test_empty_value_tensor_gives_zeros():
+    from deformops_b200.registry import msda
+
+    value = torch.zeros(2, 0, 4, 8, device="cuda", requires_grad=True)
+    shapes = torch.tensor([[3, 3]], device="cuda")
+    starts = torch.tensor([0], device="cuda")
+    loc = torch.rand(2, 5, 4, 1, 2, 2, device="cuda", requires_grad=True)
+    attn = torch.rand(2, 5, 4, 2, device="cuda", requires_grad=True)
+    out = msda(value, shapes, starts, loc, attn)
+    assert out.shape == (2, 5, 32) and (out == 0).all()
+    out.sum().backward()
+    assert (loc.grad == 0).all() and (attn.grad == 0).all() and value.grad.shape == value.shape
