@@ -268,7 +268,7 @@ def main():
     sptr = ctypes.c_void_p(stream.cuda_stream)
 
     # scratch for the replica accumulators of a 16-bit grad_value (see msda_b200_backward)
-    nscratch = 0 if args.no_scratch else shim.scratch_bytes(Bq, S, G, D, code)
+    nscratch = 0 if args.no_scratch else shim.scratch_bytes(Bq, S, G, D, Q, L, K, code)
     scratch = torch.empty(max(nscratch // 4, 1), dtype=torch.float32, device=device)
     scr = _p(scratch) if nscratch else None
 

@@ -22,7 +22,7 @@ CSRC = PKG / "csrc"
 LIB_DIR = PKG / "_lib"
 LIB_PATH = LIB_DIR / "libmsda_b200.so"
 SOURCES = ["msda_forward.cu", "msda_backward.cu", "msda_abi.cu", "msda_static_scratch.cu",
-           "msda_l2_window.cu", "msda_backward_region.cu", "msda_f64.cu"]
+           "msda_f64.cu"]
 HEADERS = [CSRC / "msda_common.cuh", PKG.parent / "include" / "msda_b200.h"]
 #: native dispatcher registration for Python-free processes (see csrc/torch_binding.cpp)
 TORCH_BINDING_PATH = LIB_DIR / "libmsda_b200_torch.so"

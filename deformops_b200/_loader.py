@@ -19,7 +19,7 @@ from .core.errors import KernelBuildError, KernelUnavailableError
 
 __all__ = ["ABI_VERSION", "Shim", "library_path", "load_library", "loaded"]
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 _lock = threading.Lock()
 _shim: "Shim | None" = None
@@ -63,7 +63,7 @@ class Shim:
                                   + [_int, _int, _int, _int, _vp])
         self.scratch_bytes = self.lib.msda_b200_backward_scratch_bytes
         self.scratch_bytes.restype = _i64
-        self.scratch_bytes.argtypes = [_i64] * 4 + [_int]
+        self.scratch_bytes.argtypes = [_i64] * 7 + [_int]
         self.forward_offsets = self.lib.msda_b200_forward_offsets
         self.forward_offsets.restype = _int
         self.forward_offsets.argtypes = ([_vp] * 4 + [_int, _vp, _int, _vp, _vp] + [_i64] * 7

@@ -1,0 +1,153 @@
+// Hardware floors of the deformable-attention kernels, measured by kernels that do nothing else.
+//
+// Built into its own library (libmsda_b200_floors.so) and loaded by bench.py only; the operator
+// library does not contain or call any of this.  Each kernel takes the addresses it touches
+// from a table the caller computes from a real workload (one 64-byte row of 32 16-bit channels
+// per bilinear corner), so the access pattern is the operator's, minus every other instruction:
+//
+//   floors_red_rows     one packed 16-byte reduction per lane into `dst`; four lanes cover a row
+//                       (what the backward's grad_value scatter costs in the L2 reduction units)
+//   floors_gather_rows  one 16-byte read-only load per lane; four lanes cover a row
+//                       (what the forward's and backward's corner gather costs in L1 / L2)
+//   floors_mma          back-to-back mma.sync m16n8k16 bf16 instructions, eight independent
+//                       accumulator sets per warp (legacy tensor-core issue rate of one SM)
+//   floors_smem_rmw     16-byte load / packed add / store on warp-private shared memory rows
+//
+// All return a CUDA error code; timing is done by the caller with events on `stream`.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+
+constexpr int kThreads = 256;
+
+// mode: 0 bf16x2, 1 f16x2
+template <int MODE>
+__global__ void __launch_bounds__(kThreads) red_rows_kernel(uint16_t *dst, const uint32_t *row_off,
+                                                          int64_t rows) {
+    const int sub = threadIdx.x & 3;
+    const int64_t stride = (int64_t)gridDim.x * (kThreads / 4);
+    const uint32_t one = MODE == 0 ? 0x3c003c00u : 0x14001400u;   // small finite addends
+    for (int64_t r = (int64_t)blockIdx.x * (kThreads / 4) + (threadIdx.x >> 2); r < rows; r += stride) {
+        uint16_t *a = dst + row_off[r] + sub * 8;
+        if (MODE == 0)
+            asm volatile("red.relaxed.gpu.global.add.noftz.v4.bf16x2 [%0], {%1, %1, %1, %1};" ::"l"(a),
+                         "r"(one));
+        else
+            asm volatile("red.relaxed.gpu.global.add.noftz.v4.f16x2 [%0], {%1, %1, %1, %1};" ::"l"(a),
+                         "r"(one));
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) gather_rows_kernel(const uint16_t *src,
+                                                             const uint32_t *row_off, int64_t rows,
+                                                             uint32_t *sink) {
+    const int sub = threadIdx.x & 3;
+    const int64_t stride = (int64_t)gridDim.x * (kThreads / 4);
+    uint32_t acc = 0;
+    for (int64_t r = (int64_t)blockIdx.x * (kThreads / 4) + (threadIdx.x >> 2); r < rows; r += stride) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(src + row_off[r] + sub * 8));
+        acc ^= v.x ^ v.y ^ v.z ^ v.w;
+    }
+    if (acc == 0x9e3779b9u) *sink = acc;   // keeps the loads alive; practically never taken
+}
+
+__global__ void __launch_bounds__(kThreads) mma_kernel(int iters, float *sink) {
+    float c[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) c[i][j] = 0.f;
+    uint32_t a0 = threadIdx.x, a1 = a0 * 3u, a2 = a0 * 5u, a3 = a0 * 7u, b0 = a0 * 11u, b1 = a0 * 13u;
+    a0 &= 0x3f803f80u; a1 &= 0x3f803f80u; a2 &= 0x3f803f80u; a3 &= 0x3f803f80u;
+    b0 &= 0x3f803f80u; b1 &= 0x3f803f80u;
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            asm volatile(
+                "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, "
+                "{%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                : "+f"(c[i][0]), "+f"(c[i][1]), "+f"(c[i][2]), "+f"(c[i][3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += c[i][0] + c[i][1] + c[i][2] + c[i][3];
+    if (s == 12345.678f) *sink = s;
+}
+
+// every warp owns `rows_per_warp` 64-byte rows of shared memory; each 4-lane slot updates a
+// pseudo-random row of its warp: 16-byte load, four packed half2 fused multiply-adds, 16-byte
+// store (the cost of accumulating one corner's grad_value contribution on chip)
+__global__ void __launch_bounds__(kThreads) smem_rmw_kernel(int iters, int rows_per_warp, uint32_t *sink) {
+    extern __shared__ uint4 rows[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane & 3, slot = lane >> 2;
+    uint4 *mine = rows + (size_t)warp * rows_per_warp * 4;
+    for (int i = lane; i < rows_per_warp * 4; i += 32) mine[i] = make_uint4(0, 0, 0, 0);
+    __syncwarp();
+    uint32_t r = (blockIdx.x * kThreads + threadIdx.x) / 4 * 2654435761u + 12345u;
+    const uint32_t m = 0x3c003c00u, w = 0x14001400u;
+    for (int it = 0; it < iters; ++it) {
+        r = r * 1664525u + 1013904223u;
+        // slots of one warp instruction take distinct rows: row index = 8 * k + slot
+        const int row = (int)(((r >> 8) % (uint32_t)(rows_per_warp / 8)) * 8 + slot);
+        uint4 v = mine[row * 4 + sub];
+        asm("fma.rn.f16x2 %0, %1, %2, %0;" : "+r"(v.x) : "r"(m), "r"(w));
+        asm("fma.rn.f16x2 %0, %1, %2, %0;" : "+r"(v.y) : "r"(m), "r"(w));
+        asm("fma.rn.f16x2 %0, %1, %2, %0;" : "+r"(v.z) : "r"(m), "r"(w));
+        asm("fma.rn.f16x2 %0, %1, %2, %0;" : "+r"(v.w) : "r"(m), "r"(w));
+        mine[row * 4 + sub] = v;
+        __syncwarp();
+    }
+    const uint4 v = mine[lane];
+    if ((v.x ^ v.y) == 0x9e3779b9u) *sink = v.x;
+}
+
+int grid_for(int ctas_per_sm) {
+    int device = 0, sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess)
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    return sms * ctas_per_sm;
+}
+
+}  // namespace
+
+extern "C" {
+
+// rows: number of 64-byte rows; row_off[i]: offset of row i in 16-bit elements from dst/src
+int floors_red_rows(void *dst, const uint32_t *row_off, int64_t rows, int f16, void *stream) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (f16)
+        red_rows_kernel<1><<<grid_for(8), kThreads, 0, s>>>(static_cast<uint16_t *>(dst), row_off, rows);
+    else
+        red_rows_kernel<0><<<grid_for(8), kThreads, 0, s>>>(static_cast<uint16_t *>(dst), row_off, rows);
+    return (int)cudaGetLastError();
+}
+
+int floors_gather_rows(const void *src, const uint32_t *row_off, int64_t rows, void *sink,
+                       void *stream) {
+    gather_rows_kernel<<<grid_for(8), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t *>(src), row_off, rows, static_cast<uint32_t *>(sink));
+    return (int)cudaGetLastError();
+}
+
+// launches sms * 4 CTAs of 8 warps; every warp issues iters * 8 instructions
+int floors_mma(int iters, void *sink, int64_t *instructions, void *stream) {
+    const int grid = grid_for(4);
+    mma_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(iters, static_cast<float *>(sink));
+    if (instructions) *instructions = (int64_t)grid * (kThreads / 32) * iters * 8;
+    return (int)cudaGetLastError();
+}
+
+// launches sms * 4 CTAs of 8 warps; every warp performs iters row updates per 4-lane slot
+int floors_smem_rmw(int iters, int rows_per_warp, void *sink, int64_t *row_updates, void *stream) {
+    const int grid = grid_for(4);
+    const size_t smem = (size_t)(kThreads / 32) * rows_per_warp * 64;
+    if (rows_per_warp < 8 || rows_per_warp % 8 != 0 || smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    smem_rmw_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        iters, rows_per_warp, static_cast<uint32_t *>(sink));
+    if (row_updates) *row_updates = (int64_t)grid * (kThreads / 4) * iters;
+    return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -3,7 +3,6 @@
 // sources/deformops/backends/cuda/include/msda_launch.cuh:63-275 without any torch type.
 #include <cstdarg>
 #include <cstdio>
-#include <cstdlib>
 
 #include "../../include/msda_b200.h"
 #include "msda_common.cuh"
@@ -171,10 +170,12 @@ int msda_b200_abi_version(void) { return MSDA_B200_ABI_VERSION; }
 
 const char *msda_b200_last_error(void) { return g_error; }
 
-int64_t msda_b200_backward_scratch_bytes(int64_t B, int64_t S, int64_t G, int64_t D, int dtype) {
+int64_t msda_b200_backward_scratch_bytes(int64_t B, int64_t S, int64_t G, int64_t D, int64_t Q,
+                                         int64_t L, int64_t K, int dtype) {
     if (dtype != MSDA_B200_F16 && dtype != MSDA_B200_BF16) return 0;
-    if (B <= 0 || S <= 0 || G <= 0 || D <= 0) return 0;
-    return B * S * G * D * (int64_t)(2 * msda_b200::kScratchImages);
+    if (B <= 0 || S <= 0 || G <= 0 || D <= 0 || Q <= 0 || L <= 0 || K <= 0) return 0;
+    return msda_b200::kScratchHeaderBytes +
+           2 * B * (S * G * D + msda_b200::extra_elems_per_sample(Q, G, D, L, K));
 }
 
 int msda_b200_launch_geometry(int64_t B, int64_t G, int64_t D, int64_t Q, int64_t L, int64_t K,
@@ -331,15 +332,13 @@ int backward_impl(const void *value, const int64_t *spatial_shapes,
             return fail(MSDA_B200_INVALID_ARGUMENT,
                         "backward: accumulating into a caller-prepared grad_value "
                         "(zero_grad_value = 0) cannot be combined with a scratch buffer");
-        const int64_t need = msda_b200_backward_scratch_bytes(B, S, G, D, dtype);
+        const int64_t need = msda_b200_backward_scratch_bytes(B, S, G, D, Q, L, K, dtype);
         if (scratch_bytes < need)
             return fail(MSDA_B200_INVALID_ARGUMENT,
                         "backward: scratch holds %lld bytes, %lld are needed",
                         (long long)scratch_bytes, (long long)need);
         if (!aligned16(scratch))
             return fail(MSDA_B200_INVALID_ARGUMENT, "backward: scratch must be 16-byte aligned");
-        if (scratch_adds < 0)
-            return fail(MSDA_B200_INVALID_ARGUMENT, "backward: scratch_adds must be >= 0");
     }
     if ((S > 0 && !grad_value) || !aligned16(grad_value))
         return fail(MSDA_B200_INVALID_ARGUMENT, "backward: grad_value is null or misaligned");
@@ -363,38 +362,28 @@ int backward_impl(const void *value, const int64_t *spatial_shapes,
     p.grad_value = grad_value;
     p.grad_loc = static_cast<float *>(grad_loc);
     p.grad_attn = grad_attn;
-    p.scratch = use_scratch ? static_cast<float *>(scratch) : nullptr;
-    p.scratch_adds = scratch_adds > 0 ? scratch_adds : (dtype == MSDA_B200_BF16 ? 12 : 256);
+    p.scratch = use_scratch ? scratch : nullptr;
+    (void)scratch_adds;   // kept in the signature for callers written against ABI 4; has no effect
 
     DeviceGuard guard(device);
     if (guard.err != cudaSuccess) return cuda_fail(guard.err, "backward: selecting the device");
     cudaError_t e;
     if (use_scratch) {
-        e = msda_b200::launch_prepare_grad_value(p, dtype, s);
+        e = msda_b200::launch_prepare_grad_value(p, dtype, apply_softmax != 0, s);
         if (e != cudaSuccess) return cuda_fail(e, "backward: clearing grad_value / scratch");
     } else if (zero_grad_value && S > 0) {
         e = cudaMemsetAsync(grad_value, 0, (size_t)(B * S * G * D) * element_size(dtype), s);
         if (e != cudaSuccess) return cuda_fail(e, "backward: clearing grad_value");
     }
     if (Q == 0) return MSDA_B200_OK;
-    // MSDA_B200_REGION_BACKWARD=1 sends encoder-shaped calls (Q == S) to the region-tiled
-    // kernel, which pre-reduces the coarse levels in shared memory.  Off by default: it cuts
-    // the L2 reduction sectors five-fold but executes 1.8x the instructions and measured
-    // 1.12 ms against 0.55 ms for the generic kernel on the headline shape.
-    static const int region_mode = [] {
-        const char *v = std::getenv("MSDA_B200_REGION_BACKWARD");
-        return v != nullptr && (v[0] == '1' || v[0] == '2') ? v[0] - '0' : 0;
-    }();
     if (dtype == MSDA_B200_F64)
         e = msda_b200::launch_backward_f64(p, apply_softmax != 0, s);
-    else if (region_mode && msda_b200::backward_region_eligible(p, dtype, apply_softmax != 0))
-        e = msda_b200::launch_backward_region(p, dtype, apply_softmax != 0, region_mode == 1, s);
     else
         e = msda_b200::launch_backward(p, dtype, apply_softmax != 0, s);
     if (e != cudaSuccess) return cuda_fail(e, "backward: kernel launch");
     if (use_scratch) {
-        e = msda_b200::launch_finalize_grad_value(p, dtype, s);
-        if (e != cudaSuccess) return cuda_fail(e, "backward: converting the scratch levels");
+        e = msda_b200::launch_finalize_grad_value(p, dtype, apply_softmax != 0, s);
+        if (e != cudaSuccess) return cuda_fail(e, "backward: converting the scratch image");
     }
     return MSDA_B200_OK;
 }

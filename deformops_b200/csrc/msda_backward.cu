@@ -19,13 +19,15 @@
 //  * softmax: weights are normalised in the pre-pass and the Jacobian is applied as
 //    p_i * (g_i - sum_j p_j g_j) before the store.
 //
-// Accuracy of 16-bit grad_value.  A coarse pyramid level receives hundreds of additions
-// per element; summing those in bf16 loses about sqrt(n) * 2^-9 of the result.  Levels
-// whose expected additions per element, 4*K*Q / (H*W), exceed `scratch_adds` are therefore
-// given several replicas in a caller-provided scratch (plan_replicas in msda_common.cuh):
-// every point adds into one replica, chosen by (query + point) mod R, with the same packed
-// 16-bit reduction as everywhere else, and finalize_kernel sums the replicas in float32.
-// prepare_kernel clears exactly what the backward kernel adds into.
+// Accuracy of 16-bit grad_value.  A coarse pyramid level receives hundreds of additions per
+// element; summing those in bf16 loses about sqrt(n) * 2^-9 of the result.  With a scratch
+// buffer the contributions are therefore scaled by a power of two and added in float16 into an
+// image held in the scratch (see "Scaled float16 accumulation" in msda_common.cuh); a level
+// that receives more than 256 additions per element gets extra replicas of itself there.
+// prepare_kernel clears what is added into and finds the magnitudes the scale is derived from,
+// finalize_kernel sums the replicas, unscales and writes grad_value in its own type.
+#include <type_traits>
+
 #include "msda_common.cuh"
 
 // tuning knobs (compile-time): points in flight together and CTAs per SM the registers allow.
@@ -42,7 +44,8 @@ namespace msda_b200 {
 
 namespace {
 
-template <typename T, bool SOFTMAX>
+// SCALED: grad_value contributions go, times 2^e, into the float16 image of the scratch
+template <typename T, bool SOFTMAX, bool SCALED>
 __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const Params p) {
     using VT = VecTraits<T>;
     constexpr int V = VT::kVec;
@@ -75,8 +78,13 @@ __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const 
 
     load_level_table(lt, p);
     __syncthreads();
-    if (threadIdx.x == 0) plan_replicas(lt, p);
-    __syncthreads();
+    float scale = 1.f;
+    if constexpr (SCALED) {
+        scale = ldexpf(1.f, grad_scale_exponent<T>(reinterpret_cast<const unsigned *>(p.scratch),
+                                                   p.Q, K, SOFTMAX));
+        if (threadIdx.x == 0) plan_replicas(lt, p);
+        __syncthreads();
+    }
 
     const int64_t total_pairs = p.B * p.Q * G;
     const int slot = lane >> p.lph_log2;
@@ -84,8 +92,13 @@ __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const 
     const T *value = reinterpret_cast<const T *>(p.value);
     const T *attn = reinterpret_cast<const T *>(p.attn);
     const T *grad_out = reinterpret_cast<const T *>(p.grad_out);
-    T *grad_value = reinterpret_cast<T *>(p.grad_value);
-    T *scratch = reinterpret_cast<T *>(p.scratch);
+    // where the packed reductions go: grad_value itself, or the float16 image in the scratch
+    using RT = typename std::conditional<SCALED, __half, T>::type;
+    RT *red_base = SCALED ? reinterpret_cast<RT *>(reinterpret_cast<char *>(p.scratch) +
+                                                   kScratchHeaderBytes)
+                          : reinterpret_cast<RT *>(p.grad_value);
+    RT *extras = red_base + p.B * p.S * (int64_t)GD;     // SCALED only: replicas of coarse levels
+    const int64_t extra_sample = extra_elems_per_sample(p.Q, G, D, p.L, K);
 
     // A CTA walks `passes` ADJACENT sets of nwarps groups; the grid covers every group.  (A
     // grid-stride loop here cost registers the kernel does not have: 0.617 ms per call with it
@@ -107,7 +120,6 @@ __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const 
         const int g = (int)(my_pair - bq * G);
         const int64_t b = bq / p.Q;
         const int64_t sample = (b * p.S * G + g) * (int64_t)D;
-        const int64_t scratch_sample = b * (int64_t)lt.scratch_sample_elems + g * D;
 
         for (int c0 = 0; c0 < P; c0 += PC) {
             const int pc = min(PC, P - c0);
@@ -134,15 +146,20 @@ __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const 
                     // a skipped point contributes exact zeros whatever its weight holds
                     const float au = (geo.flags & kInside) ? a : 0.f;
                     unsigned flags = geo.flags | ((unsigned)l << kLevelShift);
-                    unsigned red_off = (unsigned)geo.off00;         // direct: same place as value
-                    if (lt.rep[l] > 0) {
-                        // spread the additions of a coarse level over its replicas
-                        const unsigned r = (unsigned)((pair0 + sl) / G + pt) % (unsigned)lt.rep[l];
-                        red_off = lt.rep_base[l] + r * lt.level_elems[l] +
-                                  (unsigned)((geo.r0 * lt.W[l] + geo.c0) * GD);
-                        flags |= kUseScratch;
+                    unsigned red_off = (unsigned)geo.off00;         // the image: same place as value
+                    if constexpr (SCALED) {
+                        if (lt.rep[l] > 1) {
+                            // spread the additions of a coarse level over its accumulators
+                            const unsigned r = (unsigned)((pair0 + sl) / G + pt) % (unsigned)lt.rep[l];
+                            if (r > 0) {
+                                red_off = lt.rep_base[l] + (r - 1) * lt.level_elems[l] +
+                                          (unsigned)((geo.r0 * lt.W[l] + geo.c0) * GD);
+                                flags |= kUseExtra;
+                            }
+                        }
                     }
-                    A = make_uint4((unsigned)geo.off00, red_off, flags, __float_as_uint(au));
+                    // .w: the weight as the grad_value scatter uses it (times 2^e when scaled)
+                    A = make_uint4((unsigned)geo.off00, red_off, flags, __float_as_uint(au * scale));
                     Fr = make_uint4(__float_as_uint(geo.fr), __float_as_uint(geo.fc),
                                     __float_as_uint(au * dpix.x), __float_as_uint(au * dpix.y));
                 }
@@ -162,8 +179,8 @@ __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const 
                 VT::unpack(on_lane ? ld_stream16(grad_out + my_pair * D + ch)
                                    : make_uint4(0, 0, 0, 0), go);
                 const T *vc = value + sample + ch;
-                T *gc = grad_value + sample + ch;
-                T *sc = scratch + scratch_sample + ch;
+                RT *gc = red_base + sample + ch;
+                RT *xc = extras + b * extra_sample + g * D + ch;
 #pragma unroll kUnroll
                 for (int j = 0; j < pc; ++j) {
                     const uint4 A = dp[2 * j];
@@ -177,12 +194,11 @@ __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const 
                     const int rs = lt.rowstride[flags_all >> kLevelShift];
                     const int o00 = (int)A.x, o10 = o00 + rs;
                     const int off[4] = {o00, o00 + GD, o10, o10 + GD};
-                    // where the reductions go: grad_value itself, or this point's replica of
-                    // its level in the scratch (32-bit unsigned offsets; the scratch of one
-                    // sample spans up to 2*S*G*D elements)
+                    // where the reductions go (32-bit unsigned offsets, wrapping like the
+                    // corner arithmetic): the image, or this point's replica in the extras
                     const unsigned q00 = A.y, q10 = q00 + (unsigned)rs;
                     const unsigned roff[4] = {q00, q00 + (unsigned)GD, q10, q10 + (unsigned)GD};
-                    T *rbase = (flags_all & kUseScratch) ? sc : gc;
+                    RT *rbase = (flags_all & kUseExtra) ? xc : gc;
                     uint4 raw[4];
 #pragma unroll
                     for (int c = 0; c < 4; ++c) raw[c] = ldg16_if(vc + off[c], flags & (1u << c));
@@ -201,7 +217,7 @@ __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const 
                             gv[i] = fmul2(go[i], s2);
                         }
                         dot[c] = d2.x + d2.y;
-                        red_if<T>(rbase + roff[c], gv, flags & (1u << c));
+                        red_if<RT>(rbase + roff[c], gv, flags & (1u << c));
                     }
                     // derivative inside the cell [floor, floor+1); d/da = sample . grad_out
                     float gx = wr0 * (dot[1] - dot[0]) + fr * (dot[3] - dot[2]);
@@ -262,93 +278,107 @@ __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const 
     }
 }
 
-// ---- grad_value preparation and finalisation for the replica levels ----------------------------
-__device__ __forceinline__ int level_of(const LevelTable &lt, int L, int s) {
-    int l = 0;
-    for (int i = 1; i < L; ++i)
-        if (lt.H[i] > 0 && s >= lt.start[i]) l = i;   // empty levels own no position
-    return l;
+// ---- scaled float16 image: preparation and finalisation ----------------------------------------
+// largest magnitude pattern among the eight 16-bit elements of a vector
+__device__ __forceinline__ unsigned max_magnitude_bits(const uint4 &v) {
+    const unsigned a = __vmaxu2(v.x & 0x7fff7fffu, v.y & 0x7fff7fffu);
+    const unsigned b = __vmaxu2(v.z & 0x7fff7fffu, v.w & 0x7fff7fffu);
+    const unsigned m = __vmaxu2(a, b);
+    return max(m & 0xffffu, m >> 16);
 }
 
-// Clears what the backward kernel adds into: the grad_value rows of the direct levels and the
-// replica region of every sample's scratch (the grad_value rows of replica levels are written,
-// not added to, by finalize_kernel).
-template <typename T>
+// Clears the float16 image the backward kernel adds into and records the largest |grad_out|
+// (and, without softmax, |attn|) element in the scratch header.  The header cells were set to
+// zero on the stream before this kernel.
+template <bool WITH_ATTN>
 __global__ void __launch_bounds__(256) prepare_kernel(const Params p) {
-    __shared__ LevelTable lt;
-    load_level_table(lt, p);
-    __syncthreads();
-    if (threadIdx.x == 0) plan_replicas(lt, p);
-    __syncthreads();
-    constexpr int V = VecTraits<T>::kVec;
-    const int vec_per_row = p.G * p.D / V;
-    const int64_t total = p.B * p.S * vec_per_row;
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    for (int64_t v = first; v < total; v += stride) {
-        const int s = (int)((v / vec_per_row) % p.S);
-        if (lt.rep[level_of(lt, p.L, s)] == 0) reinterpret_cast<uint4 *>(p.grad_value)[v] = zero;
+    unsigned *header = reinterpret_cast<unsigned *>(p.scratch);
+    uint4 *image = reinterpret_cast<uint4 *>(reinterpret_cast<char *>(p.scratch) + kScratchHeaderBytes);
+    const int64_t image_vecs = p.B * p.S * (p.G * p.D / 8);
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    // (the extras are cleared in full: at most K*Q*G*D*L / 64 elements per sample)
+    const int64_t clear_vecs = image_vecs + p.B * (extra_elems_per_sample(p.Q, p.G, p.D, p.L, p.K) / 8);
+    for (int64_t v = first; v < clear_vecs; v += stride) image[v] = zero;
+    unsigned mg = 0, ma = 0;
+    const int64_t go_vecs = p.B * p.Q * (p.G * p.D / 8);
+    const uint4 *go = reinterpret_cast<const uint4 *>(p.grad_out);
+    for (int64_t v = first; v < go_vecs; v += stride) mg = max(mg, max_magnitude_bits(go[v]));
+    if constexpr (WITH_ATTN) {
+        // (B*Q*G*L*K 16-bit elements; the tail that does not fill a vector is read singly)
+        const int64_t n = p.B * p.Q * p.G * p.L * p.K;
+        const uint4 *at = reinterpret_cast<const uint4 *>(p.attn);
+        for (int64_t v = first; v < n / 8; v += stride) ma = max(ma, max_magnitude_bits(at[v]));
+        const unsigned short *tail = reinterpret_cast<const unsigned short *>(p.attn);
+        for (int64_t i = (n / 8) * 8 + first; i < n; i += stride) ma = max(ma, tail[i] & 0x7fffu);
     }
-    int64_t used = 0;   // replica elements per sample, contiguous from the sample's base
-    for (int l = 0; l < p.L; ++l) used += (int64_t)lt.rep[l] * lt.level_elems[l];
-    const int64_t used_vec = used / V;
-    for (int64_t v = first; v < p.B * used_vec; v += stride) {
-        const int64_t b = v / used_vec, i = v - b * used_vec;
-        reinterpret_cast<uint4 *>(reinterpret_cast<T *>(p.scratch) +
-                                  b * (int64_t)lt.scratch_sample_elems)[i] = zero;
+    mg = __reduce_max_sync(0xffffffffu, mg);
+    if ((threadIdx.x & 31) == 0 && mg != 0) atomicMax(header, mg);
+    if constexpr (WITH_ATTN) {
+        ma = __reduce_max_sync(0xffffffffu, ma);
+        if ((threadIdx.x & 31) == 0 && ma != 0) atomicMax(header + 1, ma);
     }
 }
 
-// Sums the replicas of every replica level in float32 and writes the level's grad_value rows.
-template <typename T>
+// grad_value = (image + the replicas of the position's level) * 2^-e, rounded to T
+template <typename T, bool SOFTMAX>
 __global__ void __launch_bounds__(256) finalize_kernel(const Params p) {
+    using VT = VecTraits<T>;
     __shared__ LevelTable lt;
     load_level_table(lt, p);
     __syncthreads();
     if (threadIdx.x == 0) plan_replicas(lt, p);
     __syncthreads();
-    using VT = VecTraits<T>;
-    constexpr int V = VT::kVec;
-    constexpr int NV2 = V / 2;
+    bool any_extra = false;
+    for (int l = 0; l < p.L; ++l) any_extra |= lt.rep[l] > 1;
     const int GD = p.G * p.D;
-    const int vec_per_row = GD / V;
-    const int64_t total = p.B * p.S * vec_per_row;
+    const int vec_per_row = GD / 8;
+    const int64_t extra_sample = extra_elems_per_sample(p.Q, p.G, p.D, p.L, p.K);
+    const float inv = ldexpf(1.f, -grad_scale_exponent<T>(reinterpret_cast<const unsigned *>(p.scratch),
+                                                          p.Q, p.K, SOFTMAX));
+    const float2 inv2 = make_float2(inv, inv);
+    const uint4 *image = reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(p.scratch) +
+                                                         kScratchHeaderBytes);
+    const int64_t total = p.B * p.S * (p.G * p.D / 8);
     for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < total;
          v += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t row = v / vec_per_row;
-        const int s = (int)(row % p.S);
-        const int l = level_of(lt, p.L, s);
-        const int reps = lt.rep[l];
-        if (reps == 0) continue;
-        if (s < lt.start[l] || s - lt.start[l] >= lt.H[l] * lt.W[l]) {
-            // a position outside every level (gap in a malformed table): nothing was added
-            reinterpret_cast<uint4 *>(p.grad_value)[v] = make_uint4(0u, 0u, 0u, 0u);
-            continue;
-        }
-        const int64_t b = row / p.S;
-        const T *src = reinterpret_cast<const T *>(p.scratch) + b * (int64_t)lt.scratch_sample_elems +
-                       lt.rep_base[l] + (int64_t)(s - lt.start[l]) * GD + (v - row * vec_per_row) * V;
-        float2 acc[NV2];
+        float2 f[4];
+        VecTraits<__half>::unpack(ld_stream16(image + v), f);
+        if (any_extra) {
+            const int64_t row = v / vec_per_row;
+            const int64_t b = row / p.S;
+            const int s = (int)(row - b * p.S);
+            const __half *sample_extras = reinterpret_cast<const __half *>(image) +
+                                          p.B * p.S * (int64_t)GD + b * extra_sample +
+                                          (v - row * vec_per_row) * 8;
+            // every level whose pixel range holds this position (one, for a well-formed table)
+            for (int l = 0; l < p.L; ++l) {
+                const int at = s - lt.start[l];
+                if (lt.rep[l] <= 1 || at < 0 || at >= lt.H[l] * lt.W[l]) continue;
+                const __half *src = sample_extras + lt.rep_base[l] + (int64_t)at * GD;
+                for (int r = 1; r < lt.rep[l]; ++r) {
+                    float2 x[4];
+                    VecTraits<__half>::unpack(
+                        ld_stream16(src + (int64_t)(r - 1) * lt.level_elems[l]), x);
 #pragma unroll
-        for (int i = 0; i < NV2; ++i) acc[i] = make_float2(0.f, 0.f);
-        for (int r = 0; r < reps; ++r) {
-            float2 f[NV2];
-            VT::unpack(*reinterpret_cast<const uint4 *>(src + (int64_t)r * lt.level_elems[l]), f);
-#pragma unroll
-            for (int i = 0; i < NV2; ++i) {
-                acc[i].x += f[i].x;
-                acc[i].y += f[i].y;
+                    for (int i = 0; i < 4; ++i) {
+                        f[i].x += x[i].x;
+                        f[i].y += x[i].y;
+                    }
+                }
             }
         }
-        reinterpret_cast<uint4 *>(p.grad_value)[v] = VT::pack(acc);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = fmul2(f[i], inv2);
+        reinterpret_cast<uint4 *>(p.grad_value)[v] = VT::pack(f);
     }
 }
 
-template <typename T, bool SOFTMAX>
-cudaError_t launch_typed(const Params &p, cudaStream_t stream) {
+template <typename T, bool SOFTMAX, bool SCALED>
+cudaError_t launch_kernel(const Params &p, cudaStream_t stream) {
     const size_t smem = backward_smem_bytes(p, SOFTMAX);
-    auto kernel = backward_kernel<T, SOFTMAX>;
+    auto kernel = backward_kernel<T, SOFTMAX, SCALED>;
     if (smem > 48 * 1024) {  // opt in to large dynamic shared memory only when needed
         cudaError_t e =
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -371,6 +401,14 @@ cudaError_t launch_typed(const Params &p, cudaStream_t stream) {
     q.grid = (unsigned)ctas;
     kernel<<<q.grid, q.threads, smem, stream>>>(q);
     return cudaGetLastError();
+}
+
+template <typename T, bool SOFTMAX>
+cudaError_t launch_typed(const Params &p, cudaStream_t stream) {
+    if constexpr (sizeof(T) == 2) {
+        if (p.scratch != nullptr) return launch_kernel<T, SOFTMAX, true>(p, stream);
+    }
+    return launch_kernel<T, SOFTMAX, false>(p, stream);
 }
 
 unsigned sweep_grid(const Params &p, int vec) {
@@ -402,23 +440,28 @@ cudaError_t launch_backward(const Params &p, int dtype, bool softmax, cudaStream
     }
 }
 
-cudaError_t launch_prepare_grad_value(const Params &p, int dtype, cudaStream_t stream) {
-    if (dtype == 1)
-        prepare_kernel<__half><<<sweep_grid(p, 8), 256, 0, stream>>>(p);
-    else if (dtype == 2)
-        prepare_kernel<__nv_bfloat16><<<sweep_grid(p, 8), 256, 0, stream>>>(p);
+cudaError_t launch_prepare_grad_value(const Params &p, int dtype, bool softmax, cudaStream_t stream) {
+    if (dtype != 1 && dtype != 2) return cudaErrorInvalidValue;
+    cudaError_t e = cudaMemsetAsync(p.scratch, 0, kScratchHeaderBytes, stream);
+    if (e != cudaSuccess) return e;
+    if (softmax)
+        prepare_kernel<false><<<sweep_grid(p, 8), 256, 0, stream>>>(p);
     else
-        return cudaErrorInvalidValue;
+        prepare_kernel<true><<<sweep_grid(p, 8), 256, 0, stream>>>(p);
     return cudaGetLastError();
 }
 
-cudaError_t launch_finalize_grad_value(const Params &p, int dtype, cudaStream_t stream) {
-    if (dtype == 1)
-        finalize_kernel<__half><<<sweep_grid(p, 8), 256, 0, stream>>>(p);
-    else if (dtype == 2)
-        finalize_kernel<__nv_bfloat16><<<sweep_grid(p, 8), 256, 0, stream>>>(p);
-    else
+cudaError_t launch_finalize_grad_value(const Params &p, int dtype, bool softmax, cudaStream_t stream) {
+    const unsigned grid = sweep_grid(p, 8);
+    if (dtype == 1) {
+        if (softmax) finalize_kernel<__half, true><<<grid, 256, 0, stream>>>(p);
+        else finalize_kernel<__half, false><<<grid, 256, 0, stream>>>(p);
+    } else if (dtype == 2) {
+        if (softmax) finalize_kernel<__nv_bfloat16, true><<<grid, 256, 0, stream>>>(p);
+        else finalize_kernel<__nv_bfloat16, false><<<grid, 256, 0, stream>>>(p);
+    } else {
         return cudaErrorInvalidValue;
+    }
     return cudaGetLastError();
 }
 

@@ -28,7 +28,7 @@
 namespace msda_b200 {
 
 constexpr int kMaxLevels = 16;           // level table kept in shared memory
-constexpr int kScratchImages = 6;        // 16-bit images of grad_value the backward scratch holds
+constexpr int kScratchHeaderBytes = 256;  // backward scratch: header (magnitude cells), then the image
 constexpr int kDescPerWarp = 128;        // descriptors (32 B each) a warp holds at a time
 // uint4 words of descriptor storage per warp: every slot's row is padded by one uint4 so that
 // the 8 (or fewer) slots of a warp read their 16-byte descriptor halves from distinct banks
@@ -45,8 +45,7 @@ struct Params {
     void *grad_value;       // backward only
     float *grad_loc;        // backward only
     void *grad_attn;        // backward only
-    void *scratch;          // backward only: replica accumulators (element type T), or null
-    int64_t scratch_adds;   // additions per accumulator a level may see before it gets replicas
+    void *scratch;          // backward only, 16-bit dtypes: header + scaled f16 image of grad_value, or null
     int64_t B, S, Q;
     int G, D, L, K;
     int lph_log2;           // log2(lanes per slot)
@@ -54,7 +53,6 @@ struct Params {
     int point_chunk;        // descriptors per pair held in shared memory at a time
     int64_t num_groups;     // ceil(B*Q*G / pairs per warp)
     unsigned grid;
-    int region_window_ints; // region-tiled backward: int32 window accumulators per CTA (0: none)
     int passes;             // backward: adjacent sets of groups one CTA walks (0 or 1: one)
     // Fused location arithmetic.  When `ref` is set, `loc` / `grad_loc` hold the predicted
     // offsets (B,Q,G,L,K,2) and their gradient, and a point samples at
@@ -240,6 +238,59 @@ __device__ __forceinline__ void st_stream_f2(float2 *p, float2 v) {
 }
 
 // ---------------------------------------------------------------------------------
+// Scaled float16 accumulation of a 16-bit grad_value
+// ---------------------------------------------------------------------------------
+// With a scratch buffer the 16-bit backward does not add into grad_value itself.  Every
+// contribution is multiplied by one power of two, 2^e, rounded to float16 and added (packed
+// red.global.add.f16x2) into a float16 image of grad_value that lives in the scratch; a last
+// pass multiplies by 2^-e and writes grad_value in its own type.  float16 keeps 11 significant
+// bits per addition where bfloat16 keeps 8, and the scale puts the sums where float16 can hold
+// them: e is chosen from the largest |grad_out| and |attn| element of the call (found on the
+// device, no host read) so that even Q*K contributions of the largest possible magnitude -
+// the most one element can receive - stay below the float16 maximum.
+//
+// A float16 sum of n terms still loses about sqrt(n) * 2^-12 of its value, and the coarsest
+// level of a pyramid can receive more than a thousand additions per element.  A level whose
+// elements receive n = 4*K*Q / (H*W) > kAddsPerAccumulator additions on average is therefore
+// given R = ceil(n / kAddsPerAccumulator) accumulators per element: the image itself plus R-1
+// replicas of the level in a per-sample block of "extras"; a point adds into replica
+// (query + point) mod R and the last pass sums them in float32.  Such levels are small by
+// construction: all extras of a sample take at most L * K*Q*G*D / 64 elements.
+//
+// Scratch layout: kScratchHeaderBytes of header, then the image, B*S*G*D float16, then B blocks
+// of extra_elems_per_sample() float16.  Header cell 0 / 1: the 15 magnitude bits of the largest
+// |grad_out| / |attn| element (16-bit patterns order like their magnitudes; a NaN sorts above
+// everything and switches the scaling off).
+constexpr int kAddsPerAccumulator = 256;
+constexpr int kMaxReplicas = 64;
+
+__host__ __device__ inline int64_t extra_elems_per_sample(int64_t Q, int64_t G, int64_t D,
+                                                         int64_t L, int64_t K) {
+    return L * ((((K * Q * G * D + 63) / 64) + 7) & ~(int64_t)7);   // whole 16-byte vectors
+}
+template <typename T>
+__device__ __forceinline__ float magnitude_from_bits(unsigned bits);
+template <>
+__device__ __forceinline__ float magnitude_from_bits<__nv_bfloat16>(unsigned bits) {
+    return __uint_as_float(bits << 16);
+}
+template <>
+__device__ __forceinline__ float magnitude_from_bits<__half>(unsigned bits) {
+    return __half2float(__ushort_as_half((unsigned short)bits));
+}
+
+template <typename T>
+__device__ __forceinline__ int grad_scale_exponent(const unsigned *header, int64_t Q, int K,
+                                                   bool softmax) {
+    const float mg = magnitude_from_bits<T>(header[0]);
+    const float ma = softmax ? 1.f : magnitude_from_bits<T>(header[1]);   // probabilities are <= 1
+    const float bound = mg * ma * (float)Q * (float)K;
+    if (!(bound > 0.f) || !(bound < INFINITY)) return 0;   // all zero, or inf / NaN in the inputs
+    const int e = 14 - ilogbf(bound);                      // bound * 2^e in [2^14, 2^15)
+    return e < -100 ? -100 : (e > 100 ? 100 : e);
+}
+
+// ---------------------------------------------------------------------------------
 // Level table -> shared memory (read from device memory: no host synchronisation)
 // ---------------------------------------------------------------------------------
 struct LevelTable {
@@ -247,63 +298,27 @@ struct LevelTable {
     int W[kMaxLevels];
     int start[kMaxLevels];          // first position of the level on the S axis
     int rowstride[kMaxLevels];      // elements between image rows: W * G * D
-    // backward, 16-bit grad_value: replica accumulators of the coarse levels (see
-    // plan_replicas); rep[l] == 0 means the level adds straight into grad_value
+    // scaled float16 backward: accumulators per element of the level (1 = the image only) and
+    // where the level's additional replicas start in a sample's block of extras
     int rep[kMaxLevels];
-    unsigned rep_base[kMaxLevels];     // first element of the level's replicas in a sample's scratch
-    unsigned level_elems[kMaxLevels];  // H * W * G * D
-    unsigned long long scratch_sample_elems;   // scratch elements (of T) reserved per sample
+    unsigned rep_base[kMaxLevels];
+    unsigned level_elems[kMaxLevels];   // H * W * G * D
 };
 
-// Replica plan for the 16-bit backward.  An element of level l receives n = 4*K*Q / (H*W)
-// additions on average; summed in one 16-bit accumulator they lose about sqrt(n) ulps of the
-// result (measured on B200: 4.0e-2 of the maximum at n = 336, 0.8e-2..1.1e-2 at n = 21, bf16).
-// A level with n > scratch_adds is therefore spread over R = ceil(n / scratch_adds) replica
-// accumulators in the scratch, so that no accumulator sees more than about `scratch_adds`
-// additions; every point adds into one replica and the finalize kernel sums the replicas in
-// float32.  (The loss depends on the additions per accumulator: a rule R ~ sqrt(n) was tried
-// and measured 1.2e-2 where this one gives 6.3e-3.)  All reductions stay packed 16-bit, which
-// the L2 reduction units process about three times faster per element than float32.  The
-// scratch holds kScratchImages * S*G*D elements per sample; if the plan does not fit,
-// `scratch_adds` is raised until it does.  Every kernel of one backward call derives the same
-// plan from the same level table.
+// Accumulators per level for the scaled float16 backward (see above); every kernel of a call
+// derives the same plan from the same level table.  (R-1) * H*W*G*D <= K*Q*G*D / 64 per level,
+// so the extras always fit the block extra_elems_per_sample() reserves.
 __device__ inline void plan_replicas(LevelTable &t, const Params &p) {
-    const long long GD = (long long)p.G * p.D;
-    // per sample the scratch holds kScratchImages 16-bit images of grad_value; replica offsets
-    // are 32-bit, so a plan never uses more than 2^32 - 1 elements of it
-    const long long reserved = (long long)kScratchImages * p.S * GD;
-    const long long budget = reserved < 0xffffffffll ? reserved : 0xffffffffll;
-    t.scratch_sample_elems = (unsigned long long)reserved;
-    for (int l = 0; l < p.L; ++l) {
-        t.rep[l] = 0;
-        t.rep_base[l] = 0;
-    }
-    if (p.scratch == nullptr || p.scratch_adds <= 0) return;
     const long long n4 = 4ll * p.K * p.Q;
-    long long adds = p.scratch_adds;
-    for (int iter = 0; iter < 24; ++iter) {
-        long long total = 0;
-        for (int l = 0; l < p.L; ++l) {
-            const long long hw = (long long)t.H[l] * t.W[l];
-            // R = ceil(n / adds) replicas; n <= adds: the one accumulator is grad_value itself
-            // (an empty level, hw == 0, receives nothing and gets no replicas)
-            const long long r =
-                hw > 0 && n4 > adds * hw ? (n4 + adds * hw - 1) / (adds * hw) : 0;
-            t.rep[l] = (int)r;
-            total += r * hw * GD;
-        }
-        if (total <= budget) {
-            unsigned base = 0;
-            for (int l = 0; l < p.L; ++l) {
-                t.rep_base[l] = base;
-                base += (unsigned)t.rep[l] * t.level_elems[l];
-            }
-            return;
-        }
-        const long long grow = (total + budget - 1) / budget;
-        adds = adds * (grow > 1 ? grow : 2);
+    unsigned base = 0;
+    for (int l = 0; l < p.L; ++l) {
+        const long long hw = (long long)t.H[l] * t.W[l];
+        long long r = hw > 0 ? (n4 + kAddsPerAccumulator * hw - 1) / (kAddsPerAccumulator * hw) : 1;
+        r = r < 1 ? 1 : (r > kMaxReplicas ? kMaxReplicas : r);
+        t.rep[l] = (int)r;
+        t.rep_base[l] = base;
+        base += (unsigned)(r - 1) * t.level_elems[l];
     }
-    for (int l = 0; l < p.L; ++l) t.rep[l] = 0;   // cannot happen for sane tables: all direct
 }
 
 // Loads the level table from device memory.  A level that does not lie inside the value tensor
@@ -332,7 +347,7 @@ __device__ __forceinline__ void load_level_table(LevelTable &t, const Params &p)
 enum : unsigned {
     kCorner00 = 1u, kCorner01 = 2u, kCorner10 = 4u, kCorner11 = 8u,  // corner inside the level
     kInside = 16u,       // point passes -1 <= pixel < size on both axes (NaN / inf fail)
-    kUseScratch = 32u,   // backward: this point's grad_value goes to a scratch replica
+    kUseExtra = 32u,     // backward: this point adds into a replica in the extras, not the image
     kLevelShift = 8,     // bits 8.. of the flags word carry the level index (backward)
 };
 
@@ -430,37 +445,13 @@ __host__ __device__ inline int backward_stage_floats(int pairs_per_warp, int P, 
 // launchers implemented in msda_forward.cu / msda_backward.cu; dtype: 0 f32, 1 f16, 2 bf16
 cudaError_t launch_forward(const Params &p, int dtype, bool softmax, cudaStream_t stream);
 cudaError_t launch_backward(const Params &p, int dtype, bool softmax, cudaStream_t stream);
-cudaError_t launch_prepare_grad_value(const Params &p, int dtype, cudaStream_t stream);
-cudaError_t launch_finalize_grad_value(const Params &p, int dtype, cudaStream_t stream);
+cudaError_t launch_prepare_grad_value(const Params &p, int dtype, bool softmax, cudaStream_t stream);
+cudaError_t launch_finalize_grad_value(const Params &p, int dtype, bool softmax, cudaStream_t stream);
 // float64 kernels (msda_f64.cu): loc / grad_loc point at doubles
 cudaError_t launch_forward_f64(const Params &p, bool softmax, cudaStream_t stream);
 cudaError_t launch_backward_f64(const Params &p, bool softmax, cudaStream_t stream);
 size_t forward_smem_bytes(const Params &p, bool softmax);
 size_t backward_smem_bytes(const Params &p, bool softmax);
-// region-tiled backward for encoder calls (msda_backward_region.cu)
-bool backward_region_eligible(const Params &p, int dtype, bool softmax);
-cudaError_t launch_backward_region(const Params &p, int dtype, bool softmax, bool windows,
-                                   cudaStream_t stream);
-
-// L2 access-policy window over the value tensor (msda_l2_window.cu): fills `attr` and returns
-// 1 when the opt-in feature is on, else 0
-int l2_window_attribute(const void *base, size_t bytes, cudaLaunchAttribute *attr);
-
-// launches `kernel(p)` with the value tensor's L2 window attached when there is one
-template <typename Kernel>
-inline cudaError_t launch_with_value_window(Kernel kernel, const Params &p, size_t value_bytes,
-                                            size_t smem, cudaStream_t stream) {
-    cudaLaunchAttribute attr[1];
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(p.grid);
-    cfg.blockDim = dim3((unsigned)p.threads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cfg.attrs = attr;
-    cfg.numAttrs = (unsigned)l2_window_attribute(p.value, value_bytes, attr);
-    return cudaLaunchKernelEx(&cfg, kernel, p);
-}
-
 // records `message` as the calling thread's last error (what msda_b200_last_error returns)
 // and hands `status` back; defined in msda_abi.cu next to the buffer it writes
 int set_last_error(int status, const char *message);

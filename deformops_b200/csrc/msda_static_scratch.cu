@@ -5,14 +5,16 @@
 // cudaMalloc afterwards (the call synchronises the whole device and can fail late), a plugin
 // that runs inside somebody else's step where any allocator call is off limits, or a plain C
 // caller with no caching allocator at hand.  For a 16-bit backward they still need the
-// scratch accumulators that keep the coarse pyramid levels accurate.  This entry point
-// brings its own: a fixed array that lives in the library's device image.
+// scratch image in which grad_value is accumulated accurately (scaled float16).  This entry
+// point brings its own: a fixed array that lives in the library's device image.
 //
 //  * The array is `kStaticScratchFloats` floats (32 MiB).  Every GPU on which this entry
 //    point is used holds those 32 MiB from then until the process exits.
-//  * The backward wants 12 bytes of scratch per grad_value element, so shapes with B*S*G*D
-//    above 2 796 202 elements are refused with MSDA_B200_UNSUPPORTED; use msda_b200_backward
-//    with a caller-owned scratch for those.
+//  * The backward wants msda_b200_backward_scratch_bytes(...) of scratch: 2 bytes per grad_value
+//    element, a 256-byte header and a few per cent for the replicas of coarse levels.  Shapes
+//    that need more than the 32 MiB (about 14 million grad_value elements for a three-level
+//    pyramid with Q = S) are refused with MSDA_B200_UNSUPPORTED; use msda_b200_backward with a
+//    caller-owned scratch for those.
 //  * Nothing is allocated or freed, here or further down: no cudaMalloc, no cudaFree, no
 //    library routine that allocates.  Inputs and outputs are still the caller's buffers.
 //  * The first call on a device looks up the array's device address
@@ -22,6 +24,8 @@
 //    rows a call adds into are cleared by its own prepare kernel first, so stale contents
 //    never leak into a result - but two calls whose kernels overlap on the GPU (different
 //    streams, or different host threads on the same device) race on it.  Serialise them.
+//  * Arguments are validated before the array is looked up, so a call that is refused for its
+//    shape or dtype never makes a device hold the 32 MiB.
 #include <cstdio>
 #include <mutex>
 
@@ -67,10 +71,14 @@ extern "C" int msda_b200_backward_static_scratch(
     void *grad_attn, int64_t scratch_adds, int64_t B, int64_t S, int64_t G, int64_t D, int64_t Q,
     int64_t L, int64_t K, int dtype, int apply_softmax, int device, void *stream) {
     char message[256];
-    const int64_t need = msda_b200_backward_scratch_bytes(B, S, G, D, dtype);
+    // shape / dtype checks first (they set the error message themselves)
+    const int valid = msda_b200_launch_geometry(B, G, D, Q, L, K, dtype, apply_softmax, nullptr,
+                                                nullptr, nullptr, nullptr);
+    if (valid != MSDA_B200_OK) return valid;
+    const int64_t need = msda_b200_backward_scratch_bytes(B, S, G, D, Q, L, K, dtype);
     if (need > kStaticScratchFloats * (int64_t)sizeof(float)) {
         snprintf(message, sizeof(message),
-                 "backward_static_scratch: B*S*G*D = %lld elements need %lld bytes and exceed the "
+                 "backward_static_scratch: B*S*G*D = %lld elements need %lld bytes of scratch and exceed the "
                  "built-in scratch of 32 MiB; call msda_b200_backward with a scratch buffer of "
                  "your own",
                  (long long)(B * S * G * D), (long long)need);
@@ -98,8 +106,8 @@ extern "C" int msda_b200_backward_static_scratch(
             return msda_b200::set_last_error(MSDA_B200_CUDA_ERROR, message);
         }
     }
-    // same code path as the caller-scratch entry point from here on; its prepare kernel clears
-    // the scratch rows this call accumulates into
+    // same code path as the caller-scratch entry point from here on; it clears the header and
+    // the image this call accumulates into before adding anything
     return msda_b200_backward(value, spatial_shapes, level_start_index, loc, attn, grad_out,
                               grad_value, grad_loc, grad_attn, scratch,
                               scratch ? kStaticScratchFloats * (int64_t)sizeof(float) : 0,

@@ -98,7 +98,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> backward(
     if (d.B == 0) return {grad_value, grad_loc, grad_attn};
     const int code = dtype_code(value.scalar_type());
     // replica accumulators of a 16-bit grad_value, from torch's caching allocator
-    const int64_t nbytes = d.Q > 0 ? msda_b200_backward_scratch_bytes(d.B, d.S, d.G, d.D, code) : 0;
+    const int64_t nbytes = d.Q > 0 ? msda_b200_backward_scratch_bytes(d.B, d.S, d.G, d.D, d.Q, d.L, d.K, code) : 0;
     at::Tensor scratch;
     if (nbytes > 0) scratch = at::empty({nbytes}, value.options().dtype(at::kByte));
     const int st = msda_b200_backward(

@@ -67,8 +67,9 @@ _FORWARD_INPUTS = 9
 
 
 class _LaunchCounter:
-    """Counts launches issued through this module: forward 1 kernel; backward 3 kernels
-    (prepare, backward, finalize) with the replica scratch, else 1 kernel and 1 memset."""
+    """Counts launches issued through this module: forward 1 kernel; backward with the scaled
+    float16 scratch 3 kernels (prepare, backward, finalize) and a 256-byte memset of the scratch
+    header, else 1 kernel and 1 memset of grad_value."""
 
     def __init__(self) -> None:
         self.kernels = 0
@@ -161,10 +162,10 @@ def _make_backward(softmax: bool) -> Callable[..., tuple[Tensor, Tensor, Tensor]
         shim = load_library()
         value, loc, attn, grad_output = map(_aligned, (value, loc, attn, grad_output))
         stream = torch.cuda.current_stream(value.device).cuda_stream
-        # scratch for the replica accumulators of a 16-bit grad_value; comes from torch's
-        # caching allocator, only the rows of the levels that use it are ever touched
-        nbytes = shim.scratch_bytes(B, S, G, D, DTYPE_CODES[value.dtype]) if Q > 0 else 0
-        scratch = (torch.empty(nbytes // 4, dtype=torch.float32, device=value.device)
+        # scratch of a 16-bit backward (one float16 image of grad_value plus a header); comes
+        # from torch's caching allocator, so steady-state calls reuse one block per stream
+        nbytes = shim.scratch_bytes(B, S, G, D, Q, L, K, DTYPE_CODES[value.dtype]) if Q > 0 else 0
+        scratch = (torch.empty(nbytes, dtype=torch.uint8, device=value.device)
                    if nbytes else None)
         st = shim.backward(_ptr(value), _ptr(spatial_shapes), _ptr(level_start_index), _ptr(loc),
                            _ptr(attn), _ptr(grad_output), _ptr(grad_value), _ptr(grad_loc),
@@ -174,7 +175,7 @@ def _make_backward(softmax: bool) -> Callable[..., tuple[Tensor, Tensor, Tensor]
         if st != 0:
             _raise(shim, st, "msda_b200_backward")
         launch_counter.kernels += (3 if nbytes else 1) if Q > 0 else 0
-        launch_counter.memsets += 0 if nbytes else 1
+        launch_counter.memsets += 1
         return grad_value, grad_loc, grad_attn
 
     return backward_cuda
@@ -321,8 +322,8 @@ def _offsets_backward_cuda(value, spatial_shapes, level_start_index, reference_p
     value, reference_points, offsets, attn, grad_output = map(
         _aligned, (value, reference_points, offsets, attn, grad_output))
     stream = torch.cuda.current_stream(value.device).cuda_stream
-    nbytes = shim.scratch_bytes(B, S, G, D, DTYPE_CODES[value.dtype]) if Q > 0 else 0
-    scratch = (torch.empty(nbytes // 4, dtype=torch.float32, device=value.device)
+    nbytes = shim.scratch_bytes(B, S, G, D, Q, L, K, DTYPE_CODES[value.dtype]) if Q > 0 else 0
+    scratch = (torch.empty(nbytes, dtype=torch.uint8, device=value.device)
                if nbytes else None)
     st = shim.backward_offsets(
         _ptr(value), _ptr(spatial_shapes), _ptr(level_start_index), _ptr(reference_points),
@@ -333,7 +334,7 @@ def _offsets_backward_cuda(value, spatial_shapes, level_start_index, reference_p
     if st != 0:
         _raise(shim, st, "msda_b200_backward_offsets")
     launch_counter.kernels += (3 if nbytes else 1) if Q > 0 else 0
-    launch_counter.memsets += 0 if nbytes else 1
+    launch_counter.memsets += 1
     return grad_value, grad_offsets, grad_attn
 
 

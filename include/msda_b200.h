@@ -40,7 +40,7 @@
 extern "C" {
 #endif
 
-#define MSDA_B200_ABI_VERSION 4
+#define MSDA_B200_ABI_VERSION 5
 
 /*
  * MSDA_B200_F64: value, attn, out AND loc / grad_loc are double (pass the double pointers
@@ -86,24 +86,26 @@ int msda_b200_forward(const void *value, const int64_t *spatial_shapes,
  * exact zeros).  If zero_grad_value != 0 the call first clears grad_value on `stream`;
  * pass 0 to accumulate into a buffer the caller prepared (scratch must then be NULL).
  *
- * scratch / scratch_adds (16-bit dtypes only): summing n contributions per element in
- * f16/bf16 loses about sqrt(n) ulps (2^-9 each for bf16), and a coarse pyramid level
- * receives hundreds.  When `scratch` is not NULL it must hold
- * msda_b200_backward_scratch_bytes(...) bytes.  A level whose elements receive more than
- * `scratch_adds` additions on average, n = 4*K*Q / (H*W), is then spread over
- * ceil(n / scratch_adds) replica accumulators in the scratch (same packed 16-bit
- * reductions), which are summed in float32 at the end of the call.  Pass 0 for the library
- * default (12 for bf16, 256 for f16).  Only the part of the scratch the replicas need is
- * touched.  With scratch == NULL every level adds straight into grad_value (fastest, least
- * accurate).  Ignored for float32.
+ * scratch (16-bit dtypes only): summing n contributions per element in f16/bf16 loses about
+ * sqrt(n) ulps (2^-9 each for bf16), and a coarse pyramid level receives hundreds.  When
+ * `scratch` is not NULL it must hold msda_b200_backward_scratch_bytes(...) bytes.  The call
+ * then multiplies every contribution by one power of two, chosen on the device from the
+ * largest |grad_out| and |attn| element so that no sum can leave the float16 range, adds it
+ * in float16 (11 significant bits, packed 16-byte reductions) into an image of grad_value
+ * held in the scratch (a level that receives more than 256 additions per element is given
+ * several accumulators there), and a last pass unscales the sums into grad_value in `dtype`.  With
+ * scratch == NULL every contribution is added straight into grad_value in `dtype` (least
+ * accurate for bf16).  Ignored for float32.  `scratch_adds` is accepted for callers written
+ * against ABI version 4 and has no effect.
  *
  * Replaces: boxed op `<prefix>_backward` / `<prefix>_softmax_backward`
  *   sources/deformops/backends/cuda/include/msda_boxed.cuh:32-53
  *   sources/deformops/backends/cuda/include/msda_launch.cuh:141-275 (backward_cuda)
  *   schema sources/deformops/backends/cuda/_schema.py:24-29
  * Differences: gradients and scratch are caller-allocated; grad_attn is produced directly
- * in `dtype`; accuracy comes from 16-bit replica accumulators instead of a float32 copy of
- * the whole tensor (msda_launch.cuh:188-197, 263-273 upcast, clear and cast back everything).
+ * in `dtype`; accuracy comes from scaled float16 accumulation (2 bytes per element) instead
+ * of a float32 copy of the whole tensor (msda_launch.cuh:188-197, 263-273 upcast, clear and
+ * cast back 4 bytes per element).
  */
 int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
                        const int64_t *level_start_index, const float *loc, const void *attn,
@@ -113,11 +115,14 @@ int msda_b200_backward(const void *value, const int64_t *spatial_shapes,
                        int apply_softmax, int zero_grad_value, int device, void *stream);
 
 /*
- * Bytes of scratch msda_b200_backward can use for a shape: six 16-bit images of grad_value
- * (B*S*G*D*12) for the 16-bit dtypes, 0 for float32.
+ * Bytes of scratch msda_b200_backward can use for a shape, for the 16-bit dtypes: a 256-byte
+ * header, one float16 image of grad_value (B*S*G*D*2) and, per sample, room for the extra
+ * accumulators of coarse levels (at most L * K*Q*G*D / 64 float16, a few per cent of the
+ * image when Q is about S).  0 for float32.
  * Replaces: the `new_zeros` float32 grad_value of msda_launch.cuh:188-197.
  */
-int64_t msda_b200_backward_scratch_bytes(int64_t B, int64_t S, int64_t G, int64_t D, int dtype);
+int64_t msda_b200_backward_scratch_bytes(int64_t B, int64_t S, int64_t G, int64_t D, int64_t Q,
+                                         int64_t L, int64_t K, int dtype);
 
 /*
  * Forward / backward with the caller's location arithmetic fused in.  Instead of a location
@@ -161,13 +166,14 @@ int msda_b200_backward_offsets(const void *value, const int64_t *spatial_shapes,
  * step, a C program without a caching allocator).  Same results as msda_b200_backward with a
  * scratch buffer, but the scratch is a fixed 32 MiB array inside the library: a GPU that
  * uses this entry point holds it until the process exits.
- *   - B*S*G*D above 2 796 202 elements (32 MiB / 12 bytes each; 16-bit dtypes) returns
+ *   - A shape whose msda_b200_backward_scratch_bytes(...) exceed 32 MiB (about 14 million
+ *     grad_value elements for a three-level pyramid with Q = S; 16-bit dtypes) returns
  *     MSDA_B200_UNSUPPORTED.
  *   - No cudaMalloc / cudaFree / allocating library call is made.
  *   - The first call on a device looks the array's address up (cudaGetSymbolAddress); make
  *     that first call outside any stream capture.
  *   - Every call reuses the one array, which still holds the previous call's sums; each call
- *     clears the rows it adds into.  Calls that overlap on the GPU race: serialise them.
+ *     clears what it adds into.  Calls that overlap on the GPU race: serialise them.
  *   - grad_value is always cleared (there is no accumulate mode here).
  * This entry point has no counterpart in the reference.
  */

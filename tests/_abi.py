@@ -42,16 +42,18 @@ def abi_forward(value, shapes, starts, loc, attn, *, softmax=False, stream=None)
 
 def abi_backward(value, shapes, starts, loc, attn, grad_out, *, softmax=False, zero=True,
                  scratch=True, scratch_adds=0):
-    """``scratch=True`` hands the call the replica scratch the product path uses for
-    16-bit dtypes; ``scratch=False`` forces direct 16-bit reductions on every level."""
+    """``scratch=True`` hands the call the scratch the product path uses for 16-bit dtypes
+    (scaled float16 accumulation); ``scratch=False`` adds straight into grad_value in its own
+    type.  ``scratch_adds`` is accepted by the ABI and has no effect."""
     shim = load_library()
     B, S, G, D, Q, L, K = dims(value, loc)
     # poison the outputs: the call must overwrite every element
     grad_value = torch.full_like(value, float("nan")) if zero else torch.zeros_like(value)
     grad_loc = torch.full_like(loc, float("nan"))
     grad_attn = torch.full_like(attn, float("nan"))
-    nbytes = shim.scratch_bytes(B, S, G, D, DTYPE_CODES[value.dtype]) if (scratch and zero) else 0
-    buf = torch.full((max(nbytes // 4, 1),), float("nan"), device=value.device) if nbytes else None
+    nbytes = shim.scratch_bytes(B, S, G, D, Q, L, K, DTYPE_CODES[value.dtype]) if (scratch and zero) else 0
+    # poisoned as well (0xFFFF is a NaN in both 16-bit types): the call must clear what it uses
+    buf = torch.full((nbytes,), 0xFF, dtype=torch.uint8, device=value.device) if nbytes else None
     s = torch.cuda.current_stream().cuda_stream
     st = shim.backward(_p(value), _p(shapes), _p(starts), _p(loc), _p(attn), _p(grad_out),
                        _p(grad_value), _p(grad_loc), _p(grad_attn), _p(buf), nbytes, scratch_adds,
@@ -80,8 +82,8 @@ def abi_backward_offsets(value, shapes, starts, ref, offsets, attn, grad_out, *,
     grad_value = torch.full_like(value, float("nan"))
     grad_offsets = torch.full_like(offsets, float("nan"))
     grad_attn = torch.full_like(attn, float("nan"))
-    nbytes = shim.scratch_bytes(B, S, G, D, DTYPE_CODES[value.dtype])
-    buf = torch.full((max(nbytes // 4, 1),), float("nan"), device=value.device) if nbytes else None
+    nbytes = shim.scratch_bytes(B, S, G, D, Q, L, K, DTYPE_CODES[value.dtype])
+    buf = torch.full((nbytes,), 0xFF, dtype=torch.uint8, device=value.device) if nbytes else None
     s = torch.cuda.current_stream().cuda_stream
     st = shim.backward_offsets(_p(value), _p(shapes), _p(starts), _p(ref), ref.shape[-1],
                                _p(offsets), DTYPE_CODES[offsets.dtype], _p(attn), _p(grad_out),

@@ -24,7 +24,7 @@ typedef const char *(*error_fn)(void);
 typedef int (*forward_fn)(const void *, const int64_t *, const int64_t *, const float *,
                           const void *, void *, int64_t, int64_t, int64_t, int64_t, int64_t,
                           int64_t, int64_t, int, int, int, void *);
-typedef int64_t (*scratch_fn)(int64_t, int64_t, int64_t, int64_t, int);
+typedef int64_t (*scratch_fn)(int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int);
 
 int main(int argc, char **argv) {
     void *lib = dlopen(argv[1], RTLD_NOW);
@@ -35,8 +35,8 @@ int main(int argc, char **argv) {
     scratch_fn scratch = (scratch_fn)dlsym(lib, "msda_b200_backward_scratch_bytes");
     if (!version || !last_error || !forward || !scratch) return 3;
     if (version() != MSDA_B200_ABI_VERSION) return 4;
-    if (scratch(4, 21504, 8, 32, MSDA_B200_BF16) != 4LL * 21504 * 8 * 32 * 12) return 5;
-    if (scratch(4, 21504, 8, 32, MSDA_B200_F32) != 0) return 6;
+    if (scratch(4, 21504, 8, 32, 21504, 3, 4, MSDA_B200_BF16) != 256 + 2 * 4LL * (21504 * 8 * 32 + 3 * 344064)) return 5;
+    if (scratch(4, 21504, 8, 32, 21504, 3, 4, MSDA_B200_F32) != 0) return 6;
     /* dtype 9 does not exist: refused before anything touches the GPU */
     int st = forward(0, 0, 0, 0, 0, 0, 1, 1, 1, 8, 1, 1, 1, 9, 0, 0, 0);
     if (st != MSDA_B200_INVALID_ARGUMENT) return 7;

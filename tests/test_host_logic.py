@@ -249,8 +249,8 @@ def test_host_only_entry_points():
     assert shim.launch_geometry(4, 8, 32, 21504, 3, 4, 2, 0, grid, threads, sf, sb) == 0
     assert threads.value == 256 and grid.value == 4 * 21504 // 8     # one warp per query
     assert sf.value == 8 * (2 * 128 + 32) * 16 and sb.value > sf.value   # 8 warps of descriptors
-    assert shim.scratch_bytes(4, 21504, 8, 32, 2) == 4 * 21504 * 256 * 12
-    assert shim.scratch_bytes(4, 21504, 8, 32, 0) == 0
+    assert shim.scratch_bytes(4, 21504, 8, 32, 21504, 3, 4, 2) == 256 + 2 * 4 * (21504 * 256 + 3 * 344064)
+    assert shim.scratch_bytes(4, 21504, 8, 32, 21504, 3, 4, 0) == 0
     # statuses and messages
     assert shim.launch_geometry(1, 1, 12, 1, 1, 1, 2, 0, grid, threads, sf, sb) == -2
     assert "multiple of 8" in shim.last_error()
