@@ -14,12 +14,22 @@ half-operator undefines; ``-DDEFORMOPS_NO_FP64`` as in its ahead-of-time build f
 16-bit configuration only, so that the production one also runs in float64).  The
 libraries are used by ``oracle/ref_cuda.py`` as the GPU-side parity oracle and speed bar.
 
+``stage_package`` additionally places the reference's Python package, unmodified, under
+``oracle/_ref/py/deformops`` (git-ignored like everything in ``oracle/_ref``), so that the
+machine that runs the GPU tests can import it: the tests that drive these kernels through the
+reference's own registry, layer and Hugging Face replacements, and the benchmark's reference
+arm (the reference's eager CPU path and its Triton kernels), need the real package.
+
+The reference checkout is found through ``--reference``, the environment variable
+``DEFORMOPS_REFERENCE``, or a directory ``reference`` next to this repository.
+
     python oracle/build_ref.py [--reference /path/to/reference]
 """
 
 from __future__ import annotations
 
 import argparse
+import os
 import pathlib
 import shutil
 import subprocess
@@ -27,6 +37,36 @@ import sys
 
 HERE = pathlib.Path(__file__).resolve().parent
 OUT = HERE / "_ref"
+PACKAGE_DIR = OUT / "py"
+
+
+def default_reference() -> "pathlib.Path | None":
+    """The reference checkout: ``$DEFORMOPS_REFERENCE`` or ``../reference`` beside the repo."""
+    env = os.environ.get("DEFORMOPS_REFERENCE")
+    for cand in ([pathlib.Path(env)] if env else []) + [HERE.parent.parent / "reference"]:
+        if (cand / "sources" / "deformops").is_dir():
+            return cand
+    return None
+
+
+def stage_package(reference: pathlib.Path) -> pathlib.Path:
+    """Copy ``sources/deformops`` of the checkout to ``oracle/_ref/py/deformops`` (replacing an
+    older copy) and return the directory to put on ``sys.path``."""
+    src = reference / "sources" / "deformops"
+    if not src.is_dir():
+        raise FileNotFoundError(src)
+    dst = PACKAGE_DIR / "deformops"
+    if dst.exists():
+        shutil.rmtree(dst)
+    PACKAGE_DIR.mkdir(parents=True, exist_ok=True)
+    shutil.copytree(src, dst, ignore=shutil.ignore_patterns("__pycache__", "*.pyc"))
+    return PACKAGE_DIR
+
+
+def staged_package() -> "pathlib.Path | None":
+    """``oracle/_ref/py`` if the reference package has been staged there, else None."""
+    return PACKAGE_DIR if (PACKAGE_DIR / "deformops" / "__init__.py").exists() else None
+
 UNITS = {
     "msda_fp32acc": "sources/deformops/backends/cuda/msda_fp32acc.cu",
     "msda_half2atomic": "sources/deformops/backends/cuda/experimental/msda_half2atomic.cu",
@@ -73,15 +113,17 @@ def build(reference: pathlib.Path, force: bool = False) -> list[pathlib.Path]:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=None)
     ap.add_argument("--force", action="store_true")
     args = ap.parse_args()
-    ref = pathlib.Path(args.reference)
-    if not ref.exists():
-        print(f"reference checkout {ref} not present: nothing built", file=sys.stderr)
+    ref = pathlib.Path(args.reference) if args.reference else default_reference()
+    if ref is None or not ref.exists():
+        print("no reference checkout (--reference / DEFORMOPS_REFERENCE): nothing built",
+              file=sys.stderr)
         return
     for path in build(ref, args.force):
         print(f"{path}  {path.stat().st_size / 1e6:.1f} MB")
+    print(f"staged {stage_package(ref) / 'deformops'}")
 
 
 if __name__ == "__main__":

@@ -36,6 +36,7 @@ cfg0          batch 2, levels 32/16/8 squared, 8 heads x 32, 4 points: the seede
 from __future__ import annotations
 
 import argparse
+import os
 import pathlib
 import sys
 
@@ -111,8 +112,12 @@ def save_case(name, levels, value, loc, attn_linear, attn_logits, grad_out, stor
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference/sources")
+    ap.add_argument("--reference", default=os.environ.get("DEFORMOPS_REFERENCE_SOURCES"),
+                    help="directory that holds the reference's `deformops` package (its "
+                         "`sources/`); default $DEFORMOPS_REFERENCE_SOURCES")
     args = ap.parse_args()
+    if not args.reference:
+        ap.error("pass --reference or set DEFORMOPS_REFERENCE_SOURCES")
     sys.path.insert(0, args.reference)
     torch.set_num_threads(4)
 

@@ -9,6 +9,8 @@ import subprocess
 import sys
 
 ROOT = pathlib.Path(__file__).resolve().parents[1]
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
 
 
 def _run(*args, env=None):
@@ -28,8 +30,15 @@ def test_reference_arm_prints_the_contract_line():
     assert line["value"] > 0 and line["ms_per_step"] > 0 and line["vs_baseline"] is None
     assert line["steps"] == 2 and line["warmup"] == 1 and line["n_gpus"] == 1
     assert line["config"]["workload"] == "cfg0_cpu_fp32" and line["data"] == "synthetic"
+    # same configuration keys as the GPU arm prints
+    for key in ("batch_per_gpu", "queries", "levels", "heads", "head_dim", "points"):
+        assert key in line["config"]
     base = line["cpu_baseline"]
-    assert base["kind"] == "port" and base["cores"] >= 1 and base["value"] == line["value"]
+    # the reference's own eager backend where its package was staged, else the restatement of it
+    from oracle import build_ref
+
+    assert base["kind"] == ("reference" if build_ref.staged_package() else "port")
+    assert base["cores"] >= 1 and base["value"] == line["value"]
     assert "sample" in base and base["unit"] == line["unit"]
     assert line["e2e"] == {"value": line["value"], "unit": line["unit"],
                            "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}

@@ -280,10 +280,12 @@ def test_error_message_is_thread_local():
 
 
 def test_register_into_reference_registry():
-    """With the reference checkout importable, the adapter becomes its Backend.CUDA."""
-    ref_sources = pathlib.Path("/root/reference/sources")
-    if not ref_sources.exists():
-        pytest.skip("reference checkout not present on this machine")
+    """With the reference package importable, the adapter becomes its Backend.CUDA."""
+    from oracle import build_ref
+
+    ref_sources = build_ref.staged_package()
+    if ref_sources is None:
+        pytest.skip("reference package not staged (oracle/build_ref.py needs a checkout)")
     code = (
         "import sys; sys.path.insert(0, %r)\n"
         "import torch\n"

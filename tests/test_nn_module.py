@@ -88,10 +88,12 @@ def test_sampling_location_math():
 
 
 def test_matches_reference_module_parameter_for_parameter():
-    """Where the reference checkout is importable: same init, same state-dict, same locations."""
-    ref = pathlib.Path("/root/reference/sources")
-    if not ref.exists():
-        pytest.skip("reference checkout not present on this machine")
+    """Where the reference package is importable: same init, same state-dict, same locations."""
+    from oracle import build_ref
+
+    ref = build_ref.staged_package()
+    if ref is None:
+        pytest.skip("reference package not staged (oracle/build_ref.py needs a checkout)")
     code = (
         "import sys; sys.path.insert(0, %r)\n"
         "import torch\n"
