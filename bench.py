@@ -664,7 +664,8 @@ def main():
     config4 = None
     if not args.no_config4 and CONFIG4_GLOBAL_BATCH % world == 0:
         shard = shard_batch(CONFIG4_GLOBAL_BATCH, world, rank)
-        w4 = make_workload(args.workload, batch=count, first_sample=10_000 + first, seed=0)
+        count = shard.batch
+        w4 = make_workload(args.workload, batch=count, first_sample=10_000 + shard.first_sample, seed=0)
         abi4 = AbiCall(shim, w4, device, local_rank, stream)
         d4 = abi4.buffers(w4, device)
         for _ in range(2):

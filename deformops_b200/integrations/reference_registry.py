@@ -44,9 +44,20 @@ def _load(*, download: Any = None, compile: Any = None) -> str:
 
 
 def register_into_deformops() -> Any:
-    """Register the adapter as ``Backend.CUDA`` of ``deformops.registry.msda``; returns it."""
+    """Register the adapter as ``Backend.CUDA`` of ``deformops.registry.msda``; returns it.
+
+    The reference imports its own backend adapters lazily, on the first dispatch
+    (``_dispatch.py:216-246``), and each adapter registers itself at import.  Its CUDA adapter
+    is therefore imported here first - a module is only executed once - so that this
+    registration is the one that stays."""
+    import importlib
+
     from deformops.registry import Backend as RefBackend  # type: ignore[import-not-found]
     from deformops.registry import msda as ref_msda  # type: ignore[import-not-found]
 
+    try:
+        importlib.import_module("deformops.backends.cuda.msda")
+    except Exception:  # noqa: BLE001 - an adapter that cannot import registers nothing to replace
+        pass
     ref_msda.register(RefBackend.CUDA, msda_b200_adapter, supports=supports, load=_load)
     return ref_msda

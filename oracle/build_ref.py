@@ -60,6 +60,11 @@ def stage_package(reference: pathlib.Path) -> pathlib.Path:
         shutil.rmtree(dst)
     PACKAGE_DIR.mkdir(parents=True, exist_ok=True)
     shutil.copytree(src, dst, ignore=shutil.ignore_patterns("__pycache__", "*.pyc"))
+    # the package reads its version from the checkout's VERSION file, two directories above
+    # itself, when it is not an installed distribution
+    version = reference / "VERSION"
+    if version.is_file():
+        shutil.copyfile(version, PACKAGE_DIR.parent / "VERSION")
     return PACKAGE_DIR
 
 

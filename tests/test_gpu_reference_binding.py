@@ -78,10 +78,12 @@ def test_registry_msda_with_cuda_backend_runs_these_kernels(ref, dtype, method):
     out, grads = run(Backend.CUDA)
     assert launch_counter.kernels >= 2, "the call did not reach libmsda_b200.so"
     e_out, e_grads = run(Backend.EAGER)
+    # (the eager backend computes 16-bit inputs in float32 and may return that: compare values)
+    assert out.dtype == dtype
     tol = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
-    torch.testing.assert_close(out, e_out, **tol)
-    for got, want in zip(grads, e_grads):
-        assert got.dtype == want.dtype and got.shape == want.shape
+    torch.testing.assert_close(out.float(), e_out.float(), **tol)
+    for got, want, leaf in zip(grads, e_grads, (value, loc, attn)):
+        assert got.dtype == leaf.dtype and got.shape == want.shape
         scale = want.float().abs().max().clamp_min(1e-6)
         bar = 1e-4 if dtype == torch.float32 else 2e-2
         assert ((got.float() - want.float()).abs().max() / scale).item() <= bar
