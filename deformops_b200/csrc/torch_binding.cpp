@@ -60,17 +60,24 @@ Dims check(const at::Tensor &value, const at::Tensor &shapes, const at::Tensor &
             loc.size(1),   loc.size(3),   loc.size(4)};
 }
 
+// The C ABI wants 16-byte aligned operands.  Torch's allocations are, a view at an odd storage
+// offset is not: such an operand is copied (what the Python side does as well).
+at::Tensor aligned(const at::Tensor &t) {
+    return reinterpret_cast<uintptr_t>(t.const_data_ptr()) % 16 == 0 ? t : t.clone();
+}
+
 void raise(int status, const char *what) {
     TORCH_CHECK(status == MSDA_B200_OK, what, " failed with status ", status, ": ",
                 msda_b200_last_error());
 }
 
 template <bool SOFTMAX>
-at::Tensor forward(const at::Tensor &value, const at::Tensor &shapes, const at::Tensor &starts,
-                   const at::Tensor &loc, const at::Tensor &attn, int64_t /*chunk_step*/,
+at::Tensor forward(const at::Tensor &value_in, const at::Tensor &shapes, const at::Tensor &starts,
+                   const at::Tensor &loc_in, const at::Tensor &attn_in, int64_t /*chunk_step*/,
                    int64_t K, int64_t /*channels_per_thread*/, int64_t /*threads_per_block*/) {
-    const Dims d = check(value, shapes, starts, loc, attn, K);
-    const c10::cuda::CUDAGuard guard(value.device());
+    const Dims d = check(value_in, shapes, starts, loc_in, attn_in, K);
+    const c10::cuda::CUDAGuard guard(value_in.device());
+    const at::Tensor value = aligned(value_in), loc = aligned(loc_in), attn = aligned(attn_in);
     at::Tensor out = at::empty({d.B, d.Q, d.G * d.D}, value.options());
     if (d.B == 0 || d.Q == 0) return out;
     const int st = msda_b200_forward(
@@ -84,20 +91,22 @@ at::Tensor forward(const at::Tensor &value, const at::Tensor &shapes, const at::
 
 template <bool SOFTMAX>
 std::tuple<at::Tensor, at::Tensor, at::Tensor> backward(
-    const at::Tensor &value, const at::Tensor &shapes, const at::Tensor &starts,
-    const at::Tensor &loc, const at::Tensor &attn, const at::Tensor &grad_output,
+    const at::Tensor &value_in, const at::Tensor &shapes, const at::Tensor &starts,
+    const at::Tensor &loc_in, const at::Tensor &attn_in, const at::Tensor &grad_output_in,
     int64_t /*chunk_step*/, int64_t K, int64_t /*channels_per_thread*/,
     int64_t /*threads_per_block*/) {
-    const Dims d = check(value, shapes, starts, loc, attn, K);
-    TORCH_CHECK(grad_output.scalar_type() == value.scalar_type() && grad_output.is_contiguous(),
+    const Dims d = check(value_in, shapes, starts, loc_in, attn_in, K);
+    TORCH_CHECK(grad_output_in.scalar_type() == value_in.scalar_type() && grad_output_in.is_contiguous(),
                 "deformops_b200: grad_output must be contiguous and have the value dtype");
-    const c10::cuda::CUDAGuard guard(value.device());
+    const c10::cuda::CUDAGuard guard(value_in.device());
+    const at::Tensor value = aligned(value_in), loc = aligned(loc_in), attn = aligned(attn_in),
+                     grad_output = aligned(grad_output_in);
     at::Tensor grad_value = at::empty_like(value);
     at::Tensor grad_loc = at::empty_like(loc);
     at::Tensor grad_attn = at::empty_like(attn);
     if (d.B == 0) return {grad_value, grad_loc, grad_attn};
     const int code = dtype_code(value.scalar_type());
-    // replica accumulators of a 16-bit grad_value, from torch's caching allocator
+    // scratch of a 16-bit backward (scaled float16 image), from torch's caching allocator
     const int64_t nbytes = d.Q > 0 ? msda_b200_backward_scratch_bytes(d.B, d.S, d.G, d.D, d.Q, d.L, d.K, code) : 0;
     at::Tensor scratch;
     if (nbytes > 0) scratch = at::empty({nbytes}, value.options().dtype(at::kByte));
@@ -111,6 +120,82 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> backward(
         c10::cuda::getCurrentCUDAStream().stream());
     raise(st, "msda_b200_backward");
     return {grad_value, grad_loc, grad_attn};
+}
+
+// ---- fused location arithmetic: reference points + predicted offsets instead of locations ----
+Dims check_offsets(const at::Tensor &value, const at::Tensor &shapes, const at::Tensor &starts,
+                   const at::Tensor &ref, const at::Tensor &offsets, const at::Tensor &attn) {
+    TORCH_CHECK(value.is_cuda(), "deformops_b200 kernels run on CUDA tensors only");
+    TORCH_CHECK(value.dim() == 4 && offsets.dim() == 6 && offsets.size(5) == 2 && shapes.dim() == 2 &&
+                    starts.dim() == 1,
+                "deformops_b200: value (B,S,G,D), offsets (B,Q,G,L,K,2), shapes (L,2), starts (L)");
+    TORCH_CHECK(value.scalar_type() != at::kDouble,
+                "deformops_b200: float64 values take locations, not offsets");
+    TORCH_CHECK(offsets.scalar_type() == at::kFloat || offsets.scalar_type() == value.scalar_type(),
+                "deformops_b200: offsets must be float32 or the value dtype");
+    TORCH_CHECK(attn.scalar_type() == value.scalar_type(),
+                "deformops_b200: attention weights must have the value dtype");
+    TORCH_CHECK(shapes.scalar_type() == at::kLong && starts.scalar_type() == at::kLong,
+                "deformops_b200: spatial_shapes and level_start_index must be int64");
+    TORCH_CHECK(ref.scalar_type() == at::kFloat, "deformops_b200: reference points must be float32");
+    for (const at::Tensor *t : {&value, &shapes, &starts, &ref, &offsets, &attn}) {
+        TORCH_CHECK(t->is_contiguous(), "deformops_b200: operands must be contiguous");
+        TORCH_CHECK(t->device() == value.device(), "deformops_b200: operands on different devices");
+    }
+    const Dims d{value.size(0), value.size(1), value.size(2), value.size(3),
+                 offsets.size(1), offsets.size(3), offsets.size(4)};
+    TORCH_CHECK(ref.dim() == 4 && ref.size(0) == d.B && ref.size(1) == d.Q && ref.size(2) == d.L &&
+                    (ref.size(3) == 2 || ref.size(3) == 4),
+                "deformops_b200: reference points must be (B, Q, L, 2 or 4)");
+    return d;
+}
+
+at::Tensor offsets_forward(const at::Tensor &value_in, const at::Tensor &shapes, const at::Tensor &starts,
+                           const at::Tensor &ref_in, const at::Tensor &offsets_in,
+                           const at::Tensor &attn_in, bool softmax) {
+    const Dims d = check_offsets(value_in, shapes, starts, ref_in, offsets_in, attn_in);
+    const c10::cuda::CUDAGuard guard(value_in.device());
+    const at::Tensor value = aligned(value_in), ref = aligned(ref_in), offsets = aligned(offsets_in),
+                     attn = aligned(attn_in);
+    at::Tensor out = at::empty({d.B, d.Q, d.G * d.D}, value.options());
+    if (d.B == 0 || d.Q == 0) return out;
+    const int st = msda_b200_forward_offsets(
+        value.const_data_ptr(), shapes.const_data_ptr<int64_t>(), starts.const_data_ptr<int64_t>(),
+        ref.const_data_ptr<float>(), (int)ref.size(3), offsets.const_data_ptr(),
+        dtype_code(offsets.scalar_type()), attn.const_data_ptr(), out.mutable_data_ptr(), d.B, d.S, d.G,
+        d.D, d.Q, d.L, d.K, dtype_code(value.scalar_type()), softmax, value.device().index(),
+        c10::cuda::getCurrentCUDAStream().stream());
+    raise(st, "msda_b200_forward_offsets");
+    return out;
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> offsets_backward(
+    const at::Tensor &value_in, const at::Tensor &shapes, const at::Tensor &starts,
+    const at::Tensor &ref_in, const at::Tensor &offsets_in, const at::Tensor &attn_in,
+    const at::Tensor &grad_output_in, bool softmax) {
+    const Dims d = check_offsets(value_in, shapes, starts, ref_in, offsets_in, attn_in);
+    TORCH_CHECK(grad_output_in.scalar_type() == value_in.scalar_type() && grad_output_in.is_contiguous(),
+                "deformops_b200: grad_output must be contiguous and have the value dtype");
+    const c10::cuda::CUDAGuard guard(value_in.device());
+    const at::Tensor value = aligned(value_in), ref = aligned(ref_in), offsets = aligned(offsets_in),
+                     attn = aligned(attn_in), grad_output = aligned(grad_output_in);
+    at::Tensor grad_value = at::empty_like(value);
+    at::Tensor grad_offsets = at::empty_like(offsets);
+    at::Tensor grad_attn = at::empty_like(attn);
+    if (d.B == 0) return {grad_value, grad_offsets, grad_attn};
+    const int code = dtype_code(value.scalar_type());
+    const int64_t nbytes = d.Q > 0 ? msda_b200_backward_scratch_bytes(d.B, d.S, d.G, d.D, d.Q, d.L, d.K, code) : 0;
+    at::Tensor scratch;
+    if (nbytes > 0) scratch = at::empty({nbytes}, value.options().dtype(at::kByte));
+    const int st = msda_b200_backward_offsets(
+        value.const_data_ptr(), shapes.const_data_ptr<int64_t>(), starts.const_data_ptr<int64_t>(),
+        ref.const_data_ptr<float>(), (int)ref.size(3), offsets.const_data_ptr(),
+        dtype_code(offsets.scalar_type()), attn.const_data_ptr(), grad_output.const_data_ptr(),
+        grad_value.mutable_data_ptr(), grad_offsets.mutable_data_ptr(), grad_attn.mutable_data_ptr(),
+        nbytes > 0 ? scratch.mutable_data_ptr() : nullptr, nbytes, 0, d.B, d.S, d.G, d.D, d.Q, d.L, d.K,
+        code, softmax, 1, value.device().index(), c10::cuda::getCurrentCUDAStream().stream());
+    raise(st, "msda_b200_backward_offsets");
+    return {grad_value, grad_offsets, grad_attn};
 }
 
 constexpr const char *kForwardArgs =
@@ -128,6 +213,12 @@ TORCH_LIBRARY_FRAGMENT(deformops_b200, m) {
     m.def((std::string("msda_softmax_forward") + kForwardArgs).c_str());
     m.def((std::string("msda_backward") + kBackwardArgs).c_str());
     m.def((std::string("msda_softmax_backward") + kBackwardArgs).c_str());
+    // what the default layer (fused location arithmetic) and the Hugging Face replacements call
+    m.def("msda_offsets_forward(Tensor value, Tensor spatial_shapes, Tensor level_start_index, "
+          "Tensor reference_points, Tensor offsets, Tensor attn, bool softmax) -> Tensor");
+    m.def("msda_offsets_backward(Tensor value, Tensor spatial_shapes, Tensor level_start_index, "
+          "Tensor reference_points, Tensor offsets, Tensor attn, Tensor grad_output, bool softmax) "
+          "-> (Tensor, Tensor, Tensor)");
 }
 
 TORCH_LIBRARY_IMPL(deformops_b200, CUDA, m) {
@@ -135,4 +226,6 @@ TORCH_LIBRARY_IMPL(deformops_b200, CUDA, m) {
     m.impl("msda_softmax_forward", &forward<true>);
     m.impl("msda_backward", &backward<false>);
     m.impl("msda_softmax_backward", &backward<true>);
+    m.impl("msda_offsets_forward", &offsets_forward);
+    m.impl("msda_offsets_backward", &offsets_backward);
 }

@@ -39,6 +39,7 @@ from torch.autograd.function import once_differentiable
 from ._loader import load_library
 
 __all__ = ["NAMESPACE", "OFFSETS_OPS", "PRIVATE_OPS", "PUBLIC_OPS", "DTYPE_CODES",
+           "define_reference_op_names",
            "launch_counter"]
 
 NAMESPACE = "deformops_b200"
@@ -439,6 +440,36 @@ def _define_public_ops() -> None:
         op = getattr(getattr(torch.ops, NAMESPACE), name)
         torch.library.register_vmap(f"{NAMESPACE}::{name}", _vmap_rule(op), lib=lib)
     _PUBLIC_LIBRARY = lib
+
+
+#: kept for the life of the process, like _PUBLIC_LIBRARY
+_REFERENCE_NAMES_LIBRARY: "torch.library.Library | None" = None
+
+
+def define_reference_op_names() -> bool:
+    """Offer the public operators under the REFERENCE's names as well, ``deformops::msda`` and
+    ``deformops::msda_softmax`` (same schema: ``sources/deformops/registry/msda.py:366-412``,
+    ``registry/_public_ops.py:28-67``), so that a program exported or traced against the
+    reference runs in a process that has this package but not the reference.
+
+    Explicit, not done at import: the reference defines its operators idempotently by name
+    (``_public_ops.py:58-60``), so whoever defines the names first keeps them.  Returns False,
+    and changes nothing, when the names already exist (the reference is imported)."""
+    global _REFERENCE_NAMES_LIBRARY
+    if hasattr(torch.ops, "deformops") and hasattr(torch.ops.deformops, "msda"):
+        return False
+    _define_public_ops()
+    from .core.runtime import Method
+    from .registry.msda import _public_kernel
+
+    lib = torch.library.Library("deformops", "FRAGMENT")
+    for name, method in (("msda", Method.LINEAR), ("msda_softmax", Method.SOFTMAX)):
+        lib.define(name + _PUBLIC_SCHEMA)
+        lib.impl(name, _public_kernel(method), "CompositeImplicitAutograd")
+        op = getattr(torch.ops.deformops, name)
+        torch.library.register_vmap(f"deformops::{name}", _vmap_rule(op), lib=lib)
+    _REFERENCE_NAMES_LIBRARY = lib
+    return True
 
 
 _define_private_ops()

@@ -332,3 +332,88 @@ print('python-ok')
         0, 0)
     assert torch.equal(native[1], mine[1].cpu()) and torch.equal(native[2], mine[2].cpu())
     torch.testing.assert_close(native[0], mine[0].cpu(), rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.gpu
+def test_aot_inductor_package_of_the_default_layer_runs_without_python_registration(tmp_path):
+    """The layer's default path fuses the location arithmetic into the operator
+    (``deformops_b200::msda_offsets_forward``).  A package exported from it must run in a process
+    that only loads ``libmsda_b200_torch.so``: the native library registers the offsets
+    operators too."""
+    import os
+    import shutil
+    import subprocess
+    import sys
+
+    from deformops_b200._build import TORCH_BINDING_PATH, build_torch_binding
+
+    if not TORCH_BINDING_PATH.exists():
+        build_torch_binding()
+    root = pathlib.Path(__file__).resolve().parents[1]
+    env = dict(os.environ)
+    if shutil.which("g++"):
+        env["CXX"] = shutil.which("g++")
+    compile_script = f"""
+import torch
+from deformops_b200.nn import MultiScaleDeformAttn2d
+torch.manual_seed(0)
+levels = [(8, 8), (4, 4)]
+S = sum(h * w for h, w in levels)
+layer = MultiScaleDeformAttn2d(64, num_heads=2, num_levels=2, num_points=4).cuda().eval()
+args = (torch.randn(2, S, 64, device="cuda"), torch.rand(2, S, 2, 2, device="cuda"),
+        torch.randn(2, S, 64, device="cuda"), torch.tensor(levels, device="cuda"),
+        torch.tensor([0, 64], device="cuda"))
+torch.save([a.cpu() for a in args], r'{tmp_path / 'in.pt'}')
+with torch.no_grad():
+    torch.save(layer(*args).cpu(), r'{tmp_path / 'expected.pt'}')
+    exported = torch.export.export(layer, args)
+assert any("msda_offsets_forward" in str(n.target) for n in exported.graph.nodes), exported.graph
+torch._inductor.aoti_compile_and_package(exported, package_path=r'{tmp_path / 'layer.pt2'}')
+print('compiled')
+"""
+    native_script = f"""
+import sys, torch
+torch.ops.load_library(r'{TORCH_BINDING_PATH}')
+args = tuple(a.cuda() for a in torch.load(r'{tmp_path / 'in.pt'}'))
+runner = torch._inductor.aoti_load_package(r'{tmp_path / 'layer.pt2'}')
+out = runner(*args)
+torch.cuda.synchronize()
+torch.testing.assert_close(out.cpu(), torch.load(r'{tmp_path / 'expected.pt'}'), rtol=1e-5, atol=1e-6)
+assert 'deformops_b200' not in sys.modules
+print('native-ok')
+"""
+    # (the second process starts where the package cannot even be imported from)
+    for script, word, cwd in ((compile_script, "compiled", root), (native_script, "native-ok", tmp_path)):
+        done = subprocess.run([sys.executable, "-c", script], cwd=cwd, env=env,
+                              capture_output=True, text=True, timeout=900)
+        assert done.returncode == 0 and word in done.stdout, done.stderr[-3000:]
+
+
+@pytest.mark.gpu
+def test_reference_op_names_run_these_kernels_in_a_process_without_the_reference():
+    """A program written against ``torch.ops.deformops.msda`` (the reference's public name) runs
+    on this library alone after ``define_reference_op_names()``: same numbers as our own op,
+    gradients included."""
+    import subprocess
+    import sys
+
+    code = (
+        "import torch, deformops_b200\n"
+        "from deformops_b200.ops import define_reference_op_names\n"
+        "from deformops_b200.workloads import make_workload\n"
+        "assert define_reference_op_names()\n"
+        "w = make_workload(dict(batch=2, levels=[(8, 8), (4, 4)], heads=4, head_dim=32, points=4,\n"
+        "                       dtype=torch.float32), seed=2).to('cuda')\n"
+        "def run(op, attn):\n"
+        "    leaves = [t.detach().clone().requires_grad_() for t in (w.value, w.sampling_locations, attn)]\n"
+        "    out = op(leaves[0], w.spatial_shapes, w.level_start_index, leaves[1], leaves[2])\n"
+        "    return (out, *torch.autograd.grad(out, leaves, w.grad_output))\n"
+        "for name, attn in (('msda', w.attention_weights), ('msda_softmax', w.attention_logits)):\n"
+        "    a = run(getattr(torch.ops.deformops, name), attn)\n"
+        "    b = run(getattr(torch.ops.deformops_b200, name), attn)\n"
+        "    assert all(torch.equal(x, y) for x, y in zip(a[:1] + a[2:], b[:1] + b[2:]))\n"
+        "    torch.testing.assert_close(a[1], b[1], rtol=1e-5, atol=1e-6)\n"
+        "print('ok')\n")
+    root = __import__("pathlib").Path(__file__).resolve().parents[1]
+    res = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True)
+    assert res.returncode == 0 and "ok" in res.stdout, res.stderr[-2000:]

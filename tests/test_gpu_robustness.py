@@ -187,3 +187,73 @@ def test_empty_value_tensor_gives_zeros():
     assert out.shape == (2, 5, 32) and (out == 0).all()
     out.sum().backward()
     assert (loc.grad == 0).all() and (attn.grad == 0).all() and value.grad.shape == value.shape
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_non_finite_values_next_to_unsampled_corners_never_reach_the_output(dtype):
+    """A corner outside its level, and every corner of a skipped point, is not read at all
+    (reference: ``interpolate.cuh:24-67`` skips the load): an ``inf`` stored at a level's first
+    pixel or along its border must not turn into ``0 * inf = NaN`` in queries that merely
+    touch the border from outside.  The oracle never reads such corners either."""
+    value, shapes, starts, loc, logits, grad_out = _case(
+        11, 2, 200, 4, 32, 4, [(6, 7), (3, 4)], spread=2.5)
+    # far-away points (skipped), points hugging the border from outside, points inside
+    loc[:, ::5] = 1.7
+    loc[:, 1::5, :, :, :, 0] = -0.04
+    attn = logits.softmax(-1)
+    v32 = value.clone()
+    for (h, w), first in zip(shapes.tolist(), starts.tolist()):
+        v32[:, first] = float("inf")                    # pixel (0, 0) of the level
+        v32[:, first + h * w - 1] = float("-inf")       # its last pixel
+    v, a = dev(v32, dtype), dev(attn, dtype)
+    l, sh, st = dev(loc, torch.float32), dev(shapes), dev(starts)
+    out = to_np(abi_forward(v, sh, st, l, a))
+    want = orc.forward(v.cpu(), shapes, starts, l.cpu(), a.cpu(), precision="f64")
+    finite = np.isfinite(want)
+    assert finite.any() and (~finite).any()             # the case has both kinds of query
+    assert np.array_equal(np.isfinite(out), finite)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert np.abs(out[finite] - want[finite]).max() <= tol * np.abs(want[finite]).max()
+
+
+def test_levels_listed_out_of_order_bf16_with_scratch():
+    """``level_start_index`` need not ascend: the same pyramid with its levels listed in a
+    different order (same pixels, same memory) gives the same gradients - the scratch image is
+    addressed per level, never by "the last level that starts before this row"."""
+    value, shapes, starts, loc, logits, grad_out = _case(
+        5, 2, 150, 8, 32, 4, [(12, 9), (6, 5), (3, 3)], spread=1.1)
+    attn = logits.softmax(-1)
+    perm = [2, 0, 1]
+    L, K = 3, 4
+    loc_p = loc[:, :, :, perm]
+    attn_p = attn.view(2, 150, 8, L, K)[:, :, :, perm].reshape(2, 150, 8, L * K)
+    dt = torch.bfloat16
+    v, go = dev(value, dt), dev(grad_out, dt)
+    base = abi_backward(v, dev(shapes), dev(starts), dev(loc, torch.float32), dev(attn, dt), go)
+    other = abi_backward(v, dev(shapes[perm]), dev(starts[perm]), dev(loc_p, torch.float32),
+                         dev(attn_p, dt), go)
+    truth, _, _ = orc.backward(v.cpu(), shapes, starts, loc, dev(attn, dt).cpu(), go.cpu())
+    for gv in (base[0], other[0]):
+        assert rel_err(to_np(gv), truth) <= 1e-2
+    # the location / weight gradients are the same numbers in permuted places
+    assert torch.equal(other[1], base[1][:, :, :, perm])
+    assert torch.equal(other[2].view(2, 150, 8, L, K), base[2].view(2, 150, 8, L, K)[:, :, :, perm])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("exponent", [-14, 0, 12])
+def test_grad_value_accuracy_does_not_depend_on_the_magnitude_of_grad_out(dtype, exponent):
+    """The scaled float16 accumulation picks its power of two from the largest |grad_out| of the
+    call, so a gradient 2^12 times larger (loss scaling) or 2^14 times smaller neither
+    overflows the float16 sums nor loses them to underflow: same relative error as at 1."""
+    value, shapes, starts, loc, logits, grad_out = _case(
+        9, 2, 1200, 8, 32, 4, [(20, 20), (10, 10), (5, 5)], spread=1.0)
+    attn = logits.softmax(-1)
+    scaled = grad_out * 2.0 ** exponent
+    v, a, go = dev(value, dtype), dev(attn, dtype), dev(scaled, dtype)
+    l, sh, st = dev(loc, torch.float32), dev(shapes), dev(starts)
+    gv, gl, ga = abi_backward(v, sh, st, l, a, go)
+    truth, t_gl, t_ga = orc.backward(v.cpu(), shapes, starts, l.cpu(), a.cpu(), go.cpu())
+    assert torch.isfinite(gv).all()
+    assert rel_err(to_np(gv), truth) <= 1e-2
+    assert rel_err(to_np(ga), t_ga) <= 1e-2

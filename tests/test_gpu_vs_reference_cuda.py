@@ -66,6 +66,32 @@ def test_16bit_against_reference_cuda_fp32_result(name, dtype):
     _compare(t, dtype, False, 1e-2, 1e-2)
 
 
+@pytest.mark.parametrize("batch", [16, 64])
+def test_scaling_slices_against_reference_cuda(batch):
+    """The slices a rank holds in the batch-sharded scaling sweep (global batch 64 over 8 ... 1
+    GPUs: 8, 16, 32 or 64 samples of the headline shape per GPU), in one call each: the sample
+    bases go past 2^31 bytes at these sizes and the scratch past a gigabyte.  Compared on the
+    GPU (no host copies of the gigabyte tensors) with the reference's float32 CUDA result."""
+    _, t = _inputs("cfg2_m2f_1024_bf16", torch.bfloat16, batch=batch)
+    args = (t["value"], t["shapes"], t["starts"], t["loc"], t["attn"])
+    out = abi_forward(*args)
+    gv, gl, ga = abi_backward(*args, t["grad_out"])
+    f32 = [x.float() if x.is_floating_point() else x for x in args]
+    r_out = ref_cuda.forward(*f32)
+    r_gv, r_gl, r_ga = ref_cuda.backward(*f32, t["grad_out"].float())
+
+    def err(a, b):
+        return float((a.double() - b.double()).abs().max() / b.double().abs().max())
+
+    wh = torch.flip(t["shapes"], [-1]).double()[None, None, None, :, None, :]
+    pix = t["loc"].double() * wh - 0.5
+    keep = ((pix - pix.round()).abs() >= 1e-4).all(-1, keepdim=True)
+    errs = {"out": err(out, r_out), "grad_value": err(gv, r_gv),
+            "grad_loc": err(gl * keep, r_gl * keep), "grad_attn": err(ga, r_ga)}
+    assert max(errs.values()) <= 1e-2, errs
+    assert all(torch.isfinite(x).all() for x in (out, gv, gl, ga))
+
+
 @pytest.mark.parametrize("softmax", [False, True])
 def test_float64_against_reference_cuda_float64(softmax):
     """Both implementations in double precision on the same inputs: 1e-10 (the orders of the

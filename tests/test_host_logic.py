@@ -303,3 +303,20 @@ def test_register_into_reference_registry():
     res = subprocess.run([sys.executable, "-c", code], cwd=ROOT, capture_output=True, text=True)
     assert res.returncode == 0, res.stderr[-2000:]
     assert "libmsda_b200.so" in res.stdout
+
+
+def test_reference_op_names_can_be_offered_without_the_reference():
+    """``define_reference_op_names`` defines ``deformops::msda`` / ``deformops::msda_softmax`` with
+    the public schema, once; in a fresh process so that no other test's imports interfere."""
+    code = (
+        "import torch, deformops_b200\n"
+        "from deformops_b200.ops import define_reference_op_names\n"
+        "assert define_reference_op_names() is True\n"
+        "assert define_reference_op_names() is False\n"
+        "for name in ('msda', 'msda_softmax'):\n"
+        "    ours = getattr(torch.ops.deformops_b200, name).default._schema\n"
+        "    theirs = getattr(torch.ops.deformops, name).default._schema\n"
+        "    assert str(ours).split('(', 1)[1] == str(theirs).split('(', 1)[1]\n"
+        "print('ok')\n")
+    res = subprocess.run([sys.executable, "-c", code], cwd=ROOT, capture_output=True, text=True)
+    assert res.returncode == 0 and "ok" in res.stdout, res.stderr[-2000:]
