@@ -12,9 +12,9 @@
 //      attention weight (softmax-normalised on the fly when asked);
 //   2. gather: each slot's lanes read their point's descriptor as two broadcast 16-byte
 //      shared loads, issue the four corner loads (16 bytes per lane along the head
-//      dimension; a corner outside the level, or any corner of a skipped point, is not
-//      loaded at all, exactly like the reference's im2col_bilinear) and accumulate in
-//      float32 with packed f32x2 FMAs;
+//      dimension; a corner outside the level has weight zero and its load is redirected to
+//      the nearest pixel inside, so no value is ever blended in from a clamped position)
+//      and accumulate in float32 with packed f32x2 FMAs;
 //   3. one 16-byte streaming store per lane: a warp writes a query's G*D row contiguously.
 #include "msda_common.cuh"
 
@@ -102,17 +102,18 @@ __global__ void __launch_bounds__(256, MSDA_FWD_MIN_CTAS) forward_kernel(const P
                         a = expf(a - st.x) * st.y;
                     }
                     const PointGeom geo = locate(xy.x, xy.y, lt.H[l], lt.W[l], lt.start[l], GD);
-                    // A corner that is not sampled (outside the level, or any corner of a
-                    // skipped point) gets a negative offset: its load is predicated off and
-                    // yields zeros, so nothing stored there - not even an inf or a NaN - can
-                    // reach the output.  Offsets of sampled corners are below 2^31.
-                    const unsigned f = geo.flags;
-                    const int o00 = geo.off00, o10 = geo.off00 + geo.rowstride;
-                    A = make_uint4(f & kCorner00 ? (unsigned)o00 : ~0u,
-                                   f & kCorner01 ? (unsigned)(o00 + GD) : ~0u,
-                                   f & kCorner10 ? (unsigned)o10 : ~0u,
-                                   f & kCorner11 ? (unsigned)(o10 + GD) : ~0u);
+                    // A corner outside the level keeps weight 0 and is pointed at the nearest
+                    // pixel inside it, so the gather needs no predicates; a skipped point
+                    // (geo.r0 = geo.c0 = 0, all weights 0) reads pixel (0, 0) of its level.
+                    const int H = lt.H[l], W = lt.W[l];
+                    // (an empty level has H = W = 0 and start 0: everything lands on pixel 0)
+                    const int ra = max(geo.r0, 0), rb = max(min(geo.r0 + 1, H - 1), 0);
+                    const int ca = max(geo.c0, 0), cb = max(min(geo.c0 + 1, W - 1), 0);
+                    const int row_a = (lt.start[l] + ra * W) * GD, row_b = (lt.start[l] + rb * W) * GD;
+                    A = make_uint4((unsigned)(row_a + ca * GD), (unsigned)(row_a + cb * GD),
+                                   (unsigned)(row_b + ca * GD), (unsigned)(row_b + cb * GD));
                     const float wr0 = 1.f - geo.fr, wc0 = 1.f - geo.fc;
+                    const unsigned f = geo.flags;
                     Wt = make_uint4(__float_as_uint(f & kCorner00 ? a * (wr0 * wc0) : 0.f),
                                     __float_as_uint(f & kCorner01 ? a * (wr0 * geo.fc) : 0.f),
                                     __float_as_uint(f & kCorner10 ? a * (geo.fr * wc0) : 0.f),
@@ -134,10 +135,10 @@ __global__ void __launch_bounds__(256, MSDA_FWD_MIN_CTAS) forward_kernel(const P
                 for (int j = 0; j < pc; ++j) {
                     const uint4 A = dp[2 * j];
                     const uint4 Wt = dp[2 * j + 1];
-                    const uint4 r0 = ldg16_if(vc + (int)A.x, (int)A.x >= 0);
-                    const uint4 r1 = ldg16_if(vc + (int)A.y, (int)A.y >= 0);
-                    const uint4 r2 = ldg16_if(vc + (int)A.z, (int)A.z >= 0);
-                    const uint4 r3 = ldg16_if(vc + (int)A.w, (int)A.w >= 0);
+                    const uint4 r0 = ldg16(vc + (int)A.x);
+                    const uint4 r1 = ldg16(vc + (int)A.y);
+                    const uint4 r2 = ldg16(vc + (int)A.z);
+                    const uint4 r3 = ldg16(vc + (int)A.w);
                     const uint4 raw[4] = {r0, r1, r2, r3};
                     const float w[4] = {__uint_as_float(Wt.x), __uint_as_float(Wt.y),
                                         __uint_as_float(Wt.z), __uint_as_float(Wt.w)};
