@@ -400,6 +400,7 @@ def floors_leg(w, device, stream):
     lib = ctypes.CDLL(str(build_floors_library()))
     vp, i64 = ctypes.c_void_p, ctypes.c_int64
     lib.floors_red_rows.argtypes = [vp, vp, i64, ctypes.c_int, vp]
+    lib.floors_red_rows_on.argtypes = [vp, vp, i64, ctypes.c_int, vp]
     lib.floors_gather_rows.argtypes = [vp, vp, i64, vp, vp]
     lib.floors_mma.argtypes = [ctypes.c_int, vp, ctypes.POINTER(i64), vp]
     lib.floors_smem_rmw.argtypes = [ctypes.c_int, ctypes.c_int, vp, ctypes.POINTER(i64), vp]
@@ -434,6 +435,9 @@ def floors_leg(w, device, stream):
         return statistics.median(timed_steps(lambda i: fn(), 1, stream, torch.cuda.synchronize, reps))
 
     red_ms = median_ms(lambda: lib.floors_red_rows(vp(dst.data_ptr()), vp(rows.data_ptr()), n, 1, sp))
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    red_by_sms = {str(k): n / (median_ms(lambda k=k: lib.floors_red_rows_on(
+        vp(dst.data_ptr()), vp(rows.data_ptr()), n, k, sp)) * 1e-3) for k in (sms, sms // 2, sms // 4)}
     gat_ms = median_ms(lambda: lib.floors_gather_rows(vp(src.data_ptr()), vp(rows.data_ptr()), n,
                                                       vp(sink.data_ptr()), sp))
     cnt = i64(0)
@@ -448,10 +452,13 @@ def floors_leg(w, device, stream):
         "corner_rows": n,
         "gather_rows_ms": gat_ms, "gather_rows_per_s": n / (gat_ms * 1e-3),
         "red_f16x2_rows_ms": red_ms, "red_f16x2_rows_per_s": n / (red_ms * 1e-3),
+        "red_f16x2_rows_per_s_by_issuing_sms": red_by_sms,
         "mma_m16n8k16_per_s": mma_rate,
         "smem_row_updates_per_s": rmw_rate,
         "reading": "a forward cannot finish before gather_rows_ms; a backward that adds every "
-                   "corner row into global memory cannot finish before red_f16x2_rows_ms",
+                   "corner row into global memory cannot finish before red_f16x2_rows_ms; the "
+                   "reduction rate falls in proportion to the SMs that issue, so the limit is each "
+                   "SM's path to L2 (one 64-byte row in about four cycles), not L2's reduction units",
     }
 
 

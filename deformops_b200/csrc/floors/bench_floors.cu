@@ -6,7 +6,9 @@
 // per bilinear corner), so the access pattern is the operator's, minus every other instruction:
 //
 //   floors_red_rows     one packed 16-byte reduction per lane into `dst`; four lanes cover a row
-//                       (what the backward's grad_value scatter costs in the L2 reduction units)
+//                       (what the backward's grad_value scatter costs on its way to L2)
+//   floors_red_rows_on  the same from a given number of SMs only (one CTA of 32 warps each):
+//                       shows whether the limit sits in the SMs or behind them
 //   floors_gather_rows  one 16-byte read-only load per lane; four lanes cover a row
 //                       (what the forward's and backward's corner gather costs in L1 / L2)
 //   floors_mma          back-to-back mma.sync m16n8k16 bf16 instructions, eight independent
@@ -22,13 +24,13 @@ namespace {
 constexpr int kThreads = 256;
 
 // mode: 0 bf16x2, 1 f16x2
-template <int MODE>
-__global__ void __launch_bounds__(kThreads) red_rows_kernel(uint16_t *dst, const uint32_t *row_off,
-                                                          int64_t rows) {
+template <int MODE, int THREADS>
+__global__ void __launch_bounds__(THREADS) red_rows_kernel(uint16_t *dst, const uint32_t *row_off,
+                                                         int64_t rows) {
     const int sub = threadIdx.x & 3;
-    const int64_t stride = (int64_t)gridDim.x * (kThreads / 4);
+    const int64_t stride = (int64_t)gridDim.x * (THREADS / 4);
     const uint32_t one = MODE == 0 ? 0x3c003c00u : 0x14001400u;   // small finite addends
-    for (int64_t r = (int64_t)blockIdx.x * (kThreads / 4) + (threadIdx.x >> 2); r < rows; r += stride) {
+    for (int64_t r = (int64_t)blockIdx.x * (THREADS / 4) + (threadIdx.x >> 2); r < rows; r += stride) {
         uint16_t *a = dst + row_off[r] + sub * 8;
         if (MODE == 0)
             asm volatile("red.relaxed.gpu.global.add.noftz.v4.bf16x2 [%0], {%1, %1, %1, %1};" ::"l"(a),
@@ -118,9 +120,18 @@ extern "C" {
 int floors_red_rows(void *dst, const uint32_t *row_off, int64_t rows, int f16, void *stream) {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (f16)
-        red_rows_kernel<1><<<grid_for(8), kThreads, 0, s>>>(static_cast<uint16_t *>(dst), row_off, rows);
+        red_rows_kernel<1, kThreads><<<grid_for(8), kThreads, 0, s>>>(static_cast<uint16_t *>(dst), row_off, rows);
     else
-        red_rows_kernel<0><<<grid_for(8), kThreads, 0, s>>>(static_cast<uint16_t *>(dst), row_off, rows);
+        red_rows_kernel<0, kThreads><<<grid_for(8), kThreads, 0, s>>>(static_cast<uint16_t *>(dst), row_off, rows);
+    return (int)cudaGetLastError();
+}
+
+// the float16 reductions again, issued by `sms` CTAs of 1024 threads: one CTA fills an SM, so
+// only that many SMs take part
+int floors_red_rows_on(void *dst, const uint32_t *row_off, int64_t rows, int sms, void *stream) {
+    if (sms < 1) return (int)cudaErrorInvalidValue;
+    red_rows_kernel<1, 1024><<<sms, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint16_t *>(dst), row_off, rows);
     return (int)cudaGetLastError();
 }
 
