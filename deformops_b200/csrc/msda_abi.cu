@@ -79,6 +79,8 @@ int plan(msda_b200::Params &p, int64_t B, int64_t S, int64_t G, int64_t D, int64
     const int ppw = 32 >> lg;
     const int P = (int)(L * K);
     p.point_chunk = P < msda_b200::kDescPerWarp / ppw ? P : msda_b200::kDescPerWarp / ppw;
+    if (MSDA_POINT_CHUNK_CAP > 0 && p.point_chunk > MSDA_POINT_CHUNK_CAP && lanes <= 32)
+        p.point_chunk = MSDA_POINT_CHUNK_CAP;
     if (lanes > 32 && P > p.point_chunk)
         return fail(MSDA_B200_UNSUPPORTED,
                     "D=%lld needs several channel passes and L*K=%d several point chunks; "

@@ -67,9 +67,9 @@ __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const 
     const float inv_P = 1.f / (float)P;
 
     // per-warp shared memory: descriptors, then staged gradients of the whole group
-    uint4 *desc = smem + (size_t)warp * kDescWarpVec;
+    uint4 *desc = smem + (size_t)warp * desc_warp_vec(ppw, PC);
     const int stage_floats = backward_stage_floats(ppw, P, SOFTMAX);
-    float *stage = reinterpret_cast<float *>(smem + (size_t)nwarps * kDescWarpVec) +
+    float *stage = reinterpret_cast<float *>(smem + (size_t)nwarps * desc_warp_vec(ppw, PC)) +
                    (size_t)warp * stage_floats;
     float2 *s_stats = reinterpret_cast<float2 *>(stage);         // [32] softmax (max, 1/sum)
     float2 *s_gloc = s_stats + 32;                               // [ppw*P] (dx, dy)
@@ -422,7 +422,7 @@ unsigned sweep_grid(const Params &p, int vec) {
 size_t backward_smem_bytes(const Params &p, bool softmax) {
     const size_t nwarps = p.threads / 32;
     const size_t stage_floats = backward_stage_floats(32 >> p.lph_log2, p.L * p.K, softmax);
-    return nwarps * (kDescWarpVec * 16 + stage_floats * sizeof(float));
+    return nwarps * (desc_warp_vec(32 >> p.lph_log2, p.point_chunk) * 16 + stage_floats * sizeof(float));
 }
 
 cudaError_t launch_backward(const Params &p, int dtype, bool softmax, cudaStream_t stream) {

@@ -30,9 +30,17 @@ namespace msda_b200 {
 constexpr int kMaxLevels = 16;           // level table kept in shared memory
 constexpr int kScratchHeaderBytes = 256;  // backward scratch: header (magnitude cells), then the image
 constexpr int kDescPerWarp = 128;        // descriptors (32 B each) a warp holds at a time
-// uint4 words of descriptor storage per warp: every slot's row is padded by one uint4 so that
-// the 8 (or fewer) slots of a warp read their 16-byte descriptor halves from distinct banks
-constexpr int kDescWarpVec = 2 * kDescPerWarp + 32;
+// tuning knob (compile-time): most descriptors per pair a warp holds at a time; 0 = no cap
+#ifndef MSDA_POINT_CHUNK_CAP
+#define MSDA_POINT_CHUNK_CAP 0
+#endif
+// uint4 words of descriptor storage per warp: a row of 2 * point_chunk words per slot, padded by
+// one word so that the 8 (or fewer) slots of a warp read their 16-byte descriptor halves from
+// distinct banks.  Sized to what the call needs: shared memory a CTA does not take stays L1,
+// and L1 hits are what the gather lacks.
+__host__ __device__ inline int desc_warp_vec(int pairs_per_warp, int point_chunk) {
+    return pairs_per_warp * (2 * point_chunk + 1);
+}
 
 struct Params {
     const void *value;

@@ -51,8 +51,8 @@ __global__ void __launch_bounds__(256, MSDA_FWD_MIN_CTAS) forward_kernel(const P
     const int GD = G * D;
     const float inv_K = 1.f / (float)K;
 
-    uint4 *desc = smem + (size_t)warp * kDescWarpVec;                 // [slot][PC][2]
-    float2 *stats = reinterpret_cast<float2 *>(smem + (size_t)nwarps * kDescWarpVec) +
+    uint4 *desc = smem + (size_t)warp * desc_warp_vec(ppw, PC);                 // [slot][PC][2]
+    float2 *stats = reinterpret_cast<float2 *>(smem + (size_t)nwarps * desc_warp_vec(ppw, PC)) +
                     warp * 32;                                              // softmax only
 
     load_level_table(lt, p);
@@ -192,7 +192,8 @@ cudaError_t launch_typed(const Params &p, cudaStream_t stream) {
 
 size_t forward_smem_bytes(const Params &p, bool softmax) {
     const size_t nwarps = p.threads / 32;
-    return nwarps * kDescWarpVec * 16 + (softmax ? nwarps * 32 * sizeof(float2) : 0);
+    return nwarps * desc_warp_vec(32 >> p.lph_log2, p.point_chunk) * 16 +
+           (softmax ? nwarps * 32 * sizeof(float2) : 0);
 }
 
 cudaError_t launch_forward(const Params &p, int dtype, bool softmax, cudaStream_t stream) {
