@@ -273,3 +273,28 @@ def test_grad_value_accuracy_does_not_depend_on_the_magnitude_of_grad_out(dtype,
     assert torch.isfinite(gv).all()
     assert rel_err(to_np(gv), truth) <= 1e-2
     assert rel_err(to_np(ga), t_ga) <= 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_degenerate_grad_out_zero_and_non_finite(dtype):
+    """The power of two of the float16 accumulation comes from max|grad_out|: an all-zero
+    gradient (nothing to scale by) must give exactly zero gradients, and an ``inf`` in grad_out
+    (no finite scale exists) must neither fault nor leak into samples it does not belong to."""
+    value, shapes, starts, loc, logits, grad_out = _case(
+        13, 2, 300, 8, 32, 4, [(10, 10), (5, 5)], spread=1.0)
+    attn = logits.softmax(-1)
+    v, a = dev(value, dtype), dev(attn, dtype)
+    l, sh, st = dev(loc, torch.float32), dev(shapes), dev(starts)
+    gv, gl, ga = abi_backward(v, sh, st, l, a, dev(torch.zeros_like(grad_out), dtype))
+    assert not gv.any() and not gl.any() and not ga.any()
+    bad = grad_out.clone()
+    bad[1, 7, 5] = float("inf")                              # one element of sample 1
+    gv, gl, ga = abi_backward(v, sh, st, l, a, dev(bad, dtype))
+    torch.cuda.synchronize()
+    # sample 0 never sees that element: all of its gradients stay finite and accurate
+    truth, t_gl, t_ga = orc.backward(v.cpu()[:1], shapes, starts, l.cpu()[:1], a.cpu()[:1],
+                                     dev(grad_out, dtype).cpu()[:1])
+    assert torch.isfinite(gv[0]).all() and torch.isfinite(gl[0]).all() and torch.isfinite(ga[0]).all()
+    assert rel_err(to_np(gv[:1]), truth) <= 2e-2
+    assert rel_err(to_np(ga[:1]), t_ga) <= 1e-2
+    assert not torch.isfinite(gv[1]).all()                   # and sample 1 shows it
