@@ -30,9 +30,15 @@
 
 #include "msda_common.cuh"
 
+// What bounds this kernel on B200 is not arithmetic and not DRAM but each SM's request path to
+// L2, which the gather's L1 misses share with the reductions: a kernel that issues nothing but
+// this kernel's reductions takes 0.41 ms at the headline shape (csrc/floors/bench_floors.cu),
+// this one 0.48 ms.
+//
 // tuning knobs (compile-time): points in flight together and CTAs per SM the registers allow.
-// Measured on B200 at the headline shape (backward call, ms): unroll 2 / 4 CTAs 0.583,
-// 3 / 4 0.585, 1 / 4 0.593, 1 / 3 0.604, 2 / 3 0.605, 4 / 4 0.680, 1 / 5 0.815.
+// Measured on B200 at the headline shape (backward call, ms, with an earlier accumulation scheme
+// whose extra passes cost 0.04 ms more than today's; the order is what matters): unroll 2 / 4
+// CTAs 0.583, 3 / 4 0.585, 1 / 4 0.593, 1 / 3 0.604, 2 / 3 0.605, 4 / 4 0.680, 1 / 5 0.815.
 #ifndef MSDA_BWD_UNROLL
 #define MSDA_BWD_UNROLL 2
 #endif
