@@ -293,6 +293,20 @@ __device__ __forceinline__ unsigned max_magnitude_bits(const uint4 &v) {
     return max(m & 0xffffu, m >> 16);
 }
 
+// largest magnitude pattern over vectors first, first + stride, ... of `p`: four loads in flight
+__device__ __forceinline__ unsigned scan_max_magnitude(const uint4 *__restrict__ p, int64_t n,
+                                                       int64_t first, int64_t stride) {
+    unsigned m = 0;
+    int64_t v = first;
+    for (; v + 3 * stride < n; v += 4 * stride) {
+        const uint4 a = p[v], b = p[v + stride], c = p[v + 2 * stride], d = p[v + 3 * stride];
+        m = max(max(m, max(max_magnitude_bits(a), max_magnitude_bits(b))),
+                max(max_magnitude_bits(c), max_magnitude_bits(d)));
+    }
+    for (; v < n; v += stride) m = max(m, max_magnitude_bits(p[v]));
+    return m;
+}
+
 // Clears the float16 image the backward kernel adds into and records the largest |grad_out|
 // (and, without softmax, |attn|) element in the scratch header.  The header cells were set to
 // zero on the stream before this kernel.
@@ -310,12 +324,12 @@ __global__ void __launch_bounds__(256) prepare_kernel(const Params p) {
     unsigned mg = 0, ma = 0;
     const int64_t go_vecs = p.B * p.Q * (p.G * p.D / 8);
     const uint4 *go = reinterpret_cast<const uint4 *>(p.grad_out);
-    for (int64_t v = first; v < go_vecs; v += stride) mg = max(mg, max_magnitude_bits(go[v]));
+    mg = scan_max_magnitude(go, go_vecs, first, stride);
     if constexpr (WITH_ATTN) {
         // (B*Q*G*L*K 16-bit elements; the tail that does not fill a vector is read singly)
         const int64_t n = p.B * p.Q * p.G * p.L * p.K;
         const uint4 *at = reinterpret_cast<const uint4 *>(p.attn);
-        for (int64_t v = first; v < n / 8; v += stride) ma = max(ma, max_magnitude_bits(at[v]));
+        ma = scan_max_magnitude(at, n / 8, first, stride);
         const unsigned short *tail = reinterpret_cast<const unsigned short *>(p.attn);
         for (int64_t i = (n / 8) * 8 + first; i < n; i += stride) ma = max(ma, tail[i] & 0x7fffu);
     }
@@ -347,10 +361,19 @@ __global__ void __launch_bounds__(256) finalize_kernel(const Params p) {
     const uint4 *image = reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(p.scratch) +
                                                          kScratchHeaderBytes);
     const int64_t total = p.B * p.S * (p.G * p.D / 8);
-    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < total;
-         v += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t v0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v0 < total; v0 += 4 * stride) {
+      // four vectors per turn, their image loads issued together
+      uint4 raw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+          raw[u] = v0 + u * stride < total ? ld_stream16(image + v0 + u * stride) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t v = v0 + u * stride;
+        if (v >= total) break;
         float2 f[4];
-        VecTraits<__half>::unpack(ld_stream16(image + v), f);
+        VecTraits<__half>::unpack(raw[u], f);
         if (any_extra) {
             const int64_t row = v / vec_per_row;
             const int64_t b = row / p.S;
@@ -378,6 +401,7 @@ __global__ void __launch_bounds__(256) finalize_kernel(const Params p) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) f[i] = fmul2(f[i], inv2);
         reinterpret_cast<uint4 *>(p.grad_value)[v] = VT::pack(f);
+      }
     }
 }
 
