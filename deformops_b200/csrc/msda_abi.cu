@@ -334,6 +334,12 @@ int backward_impl(const void *value, const int64_t *spatial_shapes,
             return fail(MSDA_B200_INVALID_ARGUMENT,
                         "backward: accumulating into a caller-prepared grad_value "
                         "(zero_grad_value = 0) cannot be combined with a scratch buffer");
+        // (offsets into a sample's block of extra accumulators are 32-bit)
+        if (msda_b200::extra_elems_per_sample(Q, G, D, L, K) >= ((int64_t)1 << 32))
+            return fail(MSDA_B200_UNSUPPORTED,
+                        "backward: Q*G*D*L*K = %lld is too large for the scratch layout (pass "
+                        "scratch = NULL, or split the queries)",
+                        (long long)(Q * G * D * L * K));
         const int64_t need = msda_b200_backward_scratch_bytes(B, S, G, D, Q, L, K, dtype);
         if (scratch_bytes < need)
             return fail(MSDA_B200_INVALID_ARGUMENT,
