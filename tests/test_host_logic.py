@@ -248,7 +248,8 @@ def test_host_only_entry_points():
     # headline shape: bf16, 8 heads x 32 channels, 3 levels x 4 points, 4 x 21504 queries
     assert shim.launch_geometry(4, 8, 32, 21504, 3, 4, 2, 0, grid, threads, sf, sb) == 0
     assert threads.value == 256 and grid.value == 4 * 21504 // 8     # one warp per query
-    assert sf.value == 8 * (2 * 128 + 32) * 16 and sb.value > sf.value   # 8 warps of descriptors
+    # 8 warps x 8 pairs x (12 points x 2 words + 1 word of padding) x 16 bytes of descriptors
+    assert sf.value == 8 * 8 * (2 * 12 + 1) * 16 and sb.value > sf.value
     assert shim.scratch_bytes(4, 21504, 8, 32, 21504, 3, 4, 2) == 256 + 2 * 4 * (21504 * 256 + 3 * 344064)
     assert shim.scratch_bytes(4, 21504, 8, 32, 21504, 3, 4, 0) == 0
     # statuses and messages
