@@ -55,6 +55,7 @@ METRIC = "MSDA fwd+bwd queries/sec"
 UNIT = "queries/s"
 NUM_SETS = 3  # rotating input sets
 CONFIG4_GLOBAL_BATCH = 64
+E2E_REPEATS = 5        # the end-to-end region is run this many times, the median reported
 # stated tolerances, max|a-b| / max|b|: (output, gradients)
 TOLERANCES = {torch.float32: (1e-5, 1e-4), torch.float16: (1e-2, 1e-2), torch.bfloat16: (1e-2, 1e-2)}
 
@@ -401,6 +402,7 @@ def floors_leg(w, device, stream):
     vp, i64 = ctypes.c_void_p, ctypes.c_int64
     lib.floors_red_rows.argtypes = [vp, vp, i64, ctypes.c_int, vp]
     lib.floors_red_rows_on.argtypes = [vp, vp, i64, ctypes.c_int, vp]
+    lib.floors_bulk_red_rows.argtypes = [vp, vp, i64, ctypes.c_int, vp]
     lib.floors_gather_rows.argtypes = [vp, vp, i64, vp, vp]
     lib.floors_mma.argtypes = [ctypes.c_int, vp, ctypes.POINTER(i64), vp]
     lib.floors_smem_rmw.argtypes = [ctypes.c_int, ctypes.c_int, vp, ctypes.POINTER(i64), vp]
@@ -438,6 +440,10 @@ def floors_leg(w, device, stream):
     sms = torch.cuda.get_device_properties(device).multi_processor_count
     red_by_sms = {str(k): n / (median_ms(lambda k=k: lib.floors_red_rows_on(
         vp(dst.data_ptr()), vp(rows.data_ptr()), n, k, sp)) * 1e-3) for k in (sms, sms // 2, sms // 4)}
+    if lib.floors_bulk_red_rows(vp(dst.data_ptr()), vp(rows.data_ptr()), n, 1, sp) != 0:
+        raise RuntimeError("floors_bulk_red_rows refused its arguments")
+    bulk_by_piece = {str(64 * k): n // 8 * 8 / (median_ms(lambda k=k: lib.floors_bulk_red_rows(
+        vp(dst.data_ptr()), vp(rows.data_ptr()), n, k, sp)) * 1e-3) for k in (1, 2, 4)}
     gat_ms = median_ms(lambda: lib.floors_gather_rows(vp(src.data_ptr()), vp(rows.data_ptr()), n,
                                                       vp(sink.data_ptr()), sp))
     cnt = i64(0)
@@ -453,12 +459,14 @@ def floors_leg(w, device, stream):
         "gather_rows_ms": gat_ms, "gather_rows_per_s": n / (gat_ms * 1e-3),
         "red_f16x2_rows_ms": red_ms, "red_f16x2_rows_per_s": n / (red_ms * 1e-3),
         "red_f16x2_rows_per_s_by_issuing_sms": red_by_sms,
+        "bulk_reduce_f16_rows_per_s_by_piece_bytes": bulk_by_piece,
         "mma_m16n8k16_per_s": mma_rate,
         "smem_row_updates_per_s": rmw_rate,
         "reading": "a forward cannot finish before gather_rows_ms; a backward that adds every "
                    "corner row into global memory cannot finish before red_f16x2_rows_ms; the "
                    "reduction rate falls in proportion to the SMs that issue, so the limit is each "
-                   "SM's path to L2 (one 64-byte row in about four cycles), not L2's reduction units",
+                   "SM's path to L2 (one 64-byte row in about four cycles), not L2's reduction units; "
+                   "the copy engine's bulk reductions leave the SM no faster",
     }
 
 
@@ -542,7 +550,6 @@ def main():
         return
 
     from deformops_b200._loader import load_library
-    from deformops_b200.ops import launch_counter
     from deformops_b200.registry import Backend, msda
     from deformops_b200.sharding import shard_batch
     from deformops_b200.workloads import CONFIGS, make_workload
@@ -650,9 +657,12 @@ def main():
         e2e_steps = max(3, min(args.steps, 20))
         for i in range(3):
             e2e_step(hosts[i % NUM_SETS], sets[i % NUM_SETS])
-        launch_counter.reset()
-        e2e_ms = timed_steps(lambda i: e2e_step(hosts[i % NUM_SETS], sets[i % NUM_SETS]), e2e_steps,
-                             stream, barrier)[0] / e2e_steps
+        # the host side (other tenants of the machine, the allocator) makes this leg noisier than
+        # the device-timed one: several repeats, the median reported with the spread beside it
+        e2e_all = [t / e2e_steps for t in timed_steps(
+            lambda i: e2e_step(hosts[i % NUM_SETS], sets[i % NUM_SETS]), e2e_steps, stream, barrier,
+            E2E_REPEATS)]
+        e2e_ms = statistics.median(e2e_all)
         # the host buffers must hold what the resident path computes for the same inputs
         last = sets[(e2e_steps - 1) % NUM_SETS]
         abi.step(last)
@@ -660,11 +670,14 @@ def main():
         if not (torch.equal(sink["out"], last["out"].cpu())
                 and torch.equal(sink["grad_loc"], last["grad_loc"].cpu())):
             raise RuntimeError("e2e leg: results on the host differ from the resident path")
-        copy_ms = timed_steps(lambda i: e2e_step(hosts[i % NUM_SETS], sets[i % NUM_SETS], False),
-                              e2e_steps, stream, barrier)[0] / e2e_steps
+        copy_all = [t / e2e_steps for t in timed_steps(
+            lambda i: e2e_step(hosts[i % NUM_SETS], sets[i % NUM_SETS], False), e2e_steps, stream,
+            barrier, E2E_REPEATS)]
+        copy_ms = statistics.median(copy_all)
         h2d = sum(h.numel() * h.element_size() for h in hosts[0].values())
         d2h = sum(t.numel() * t.element_size() for t in sink.values())
-        e2e = {"ms": e2e_ms, "copy_ms": copy_ms, "h2d": h2d, "d2h": d2h, "steps": e2e_steps}
+        e2e = {"ms": e2e_ms, "copy_ms": copy_ms, "h2d": h2d, "d2h": d2h, "steps": e2e_steps,
+               "ms_all": e2e_all, "copy_all": copy_all}
         del sink
 
     # ---- config 4: global batch 64 over the ranks, timed and checked per rank --------------------
@@ -793,7 +806,9 @@ def main():
         if e2e:
             line["e2e"] = {"value": queries / (e2e_ms * 1e-3), "unit": UNIT,
                            "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
-                           "ms_per_step": e2e_ms, "steps": e2e["steps"],
+                           "ms_per_step": e2e_ms, "steps": e2e["steps"], "repeats": E2E_REPEATS,
+                           "ms_per_step_repeats_rank0": [round(t, 4) for t in e2e["ms_all"]],
+                           "copy_only_ms_per_step_repeats_rank0": [round(t, 4) for t in e2e["copy_all"]],
                            "api": "deformops_b200.registry.msda + autograd, pinned host buffers",
                            "pipeline": "per-sample chunks; upload, kernels and download on three streams",
                            "copy_only_ms_per_step": copy_ms,

@@ -9,6 +9,10 @@
 //                       (what the backward's grad_value scatter costs on its way to L2)
 //   floors_red_rows_on  the same from a given number of SMs only (one CTA of 32 warps each):
 //                       shows whether the limit sits in the SMs or behind them
+//   floors_bulk_red_rows  the same additions sent by the copy engine instead of the load/store
+//                       unit: the warp stages its rows in shared memory and one lane per piece
+//                       of 1, 2 or 4 adjacent rows issues cp.reduce.async.bulk (shows whether
+//                       the other way out of the SM is any wider)
 //   floors_gather_rows  one 16-byte read-only load per lane; four lanes cover a row
 //                       (what the forward's and backward's corner gather costs in L1 / L2)
 //   floors_mma          back-to-back mma.sync m16n8k16 bf16 instructions, eight independent
@@ -39,6 +43,43 @@ __global__ void __launch_bounds__(THREADS) red_rows_kernel(uint16_t *dst, const 
             asm volatile("red.relaxed.gpu.global.add.noftz.v4.f16x2 [%0], {%1, %1, %1, %1};" ::"l"(a),
                          "r"(one));
     }
+}
+
+// RPP adjacent 64-byte rows per bulk reduction; a warp turn stages eight rows (512 bytes) in one
+// of NS ring slots and 8 / RPP lanes send them.  The waits are the bulk-group waits of the
+// issuing lanes on their own groups: they end when the engine has read the slot.
+template <int RPP>
+__global__ void __launch_bounds__(kThreads) bulk_red_rows_kernel(uint16_t *dst, const uint32_t *row_off,
+                                                               int64_t rows) {
+    constexpr int NS = 4;
+    constexpr int OPS = 8 / RPP;
+    constexpr int PIECE = RPP * 64;
+    __shared__ __align__(128) unsigned char stage[kThreads / 32][NS][512];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int64_t turns = rows / 8;
+    const int64_t stride = (int64_t)gridDim.x * (kThreads / 32);
+    const uint4 addend = make_uint4(0x14001400u, 0x14001400u, 0x14001400u, 0x14001400u);
+    int slot = 0;
+    for (int64_t t = (int64_t)blockIdx.x * (kThreads / 32) + w; t < turns; t += stride) {
+        if (lane < OPS) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(NS - 1) : "memory");
+        __syncwarp();
+        *reinterpret_cast<uint4 *>(&stage[w][slot][lane * 16]) = addend;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane < OPS) {
+            // the piece that holds this lane's first row, at a multiple of the piece size
+            const uint32_t first = row_off[t * 8 + lane * RPP] / (32u * RPP) * (32u * RPP);
+            const uint32_t src = (uint32_t)__cvta_generic_to_shared(&stage[w][slot][lane * PIECE]);
+            asm volatile(
+                "cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.f16 [%0], [%1], %2;" ::"l"(
+                    dst + first),
+                "r"(src), "n"(PIECE)
+                : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        slot = (slot + 1) % NS;
+    }
+    if (lane < OPS) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
 __global__ void __launch_bounds__(kThreads) gather_rows_kernel(const uint16_t *src,
@@ -132,6 +173,22 @@ int floors_red_rows_on(void *dst, const uint32_t *row_off, int64_t rows, int sms
     if (sms < 1) return (int)cudaErrorInvalidValue;
     red_rows_kernel<1, 1024><<<sms, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<uint16_t *>(dst), row_off, rows);
+    return (int)cudaGetLastError();
+}
+
+// rows_per_piece 1, 2 or 4; `dst` must hold a multiple of four rows and every row_off a multiple
+// of 32 (a 64-byte row), which the caller's table of bilinear corner rows does
+int floors_bulk_red_rows(void *dst, const uint32_t *row_off, int64_t rows, int rows_per_piece,
+                         void *stream) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    uint16_t *d = static_cast<uint16_t *>(dst);
+    if ((reinterpret_cast<uintptr_t>(dst) & 255) != 0) return (int)cudaErrorInvalidValue;
+    switch (rows_per_piece) {
+        case 1: bulk_red_rows_kernel<1><<<grid_for(4), kThreads, 0, s>>>(d, row_off, rows); break;
+        case 2: bulk_red_rows_kernel<2><<<grid_for(4), kThreads, 0, s>>>(d, row_off, rows); break;
+        case 4: bulk_red_rows_kernel<4><<<grid_for(4), kThreads, 0, s>>>(d, row_off, rows); break;
+        default: return (int)cudaErrorInvalidValue;
+    }
     return (int)cudaGetLastError();
 }
 
