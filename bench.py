@@ -404,6 +404,7 @@ def floors_leg(w, device, stream):
     lib.floors_red_rows_on.argtypes = [vp, vp, i64, ctypes.c_int, vp]
     lib.floors_bulk_red_rows.argtypes = [vp, vp, i64, ctypes.c_int, vp]
     lib.floors_gather_rows.argtypes = [vp, vp, i64, vp, vp]
+    lib.floors_gather_red_rows.argtypes = [vp, vp, vp, i64, ctypes.c_int, vp]
     lib.floors_mma.argtypes = [ctypes.c_int, vp, ctypes.POINTER(i64), vp]
     lib.floors_smem_rmw.argtypes = [ctypes.c_int, ctypes.c_int, vp, ctypes.POINTER(i64), vp]
     B, S, G, D, Q, L, K = w.dims
@@ -446,6 +447,20 @@ def floors_leg(w, device, stream):
         vp(dst.data_ptr()), vp(rows.data_ptr()), n, k, sp)) * 1e-3) for k in (1, 2, 4)}
     gat_ms = median_ms(lambda: lib.floors_gather_rows(vp(src.data_ptr()), vp(rows.data_ptr()), n,
                                                       vp(sink.data_ptr()), sp))
+    # with the shared memory the backward kernel holds per CTA at this shape, so that L1 is as small
+    from deformops_b200._loader import load_library
+    from deformops_b200.ops import DTYPE_CODES
+
+    grid_, threads_, smem_f, smem_b = ctypes.c_int64(), ctypes.c_int(), ctypes.c_int64(), ctypes.c_int64()
+    if load_library().launch_geometry(B, G, D, Q, L, K, DTYPE_CODES[w.value.dtype], 0, grid_, threads_,
+                                      smem_f, smem_b) != 0:
+        raise RuntimeError("launch geometry refused the workload's shape")
+    bwd_smem = min(int(smem_b.value), 48 * 1024)
+    if lib.floors_gather_red_rows(vp(src.data_ptr()), vp(dst.data_ptr()), vp(rows.data_ptr()), n,
+                                  bwd_smem, sp) != 0:
+        raise RuntimeError("floors_gather_red_rows refused its arguments")
+    both_ms = median_ms(lambda: lib.floors_gather_red_rows(vp(src.data_ptr()), vp(dst.data_ptr()),
+                                                           vp(rows.data_ptr()), n, bwd_smem, sp))
     cnt = i64(0)
     mma_ms = median_ms(lambda: lib.floors_mma(2000, vp(sink.data_ptr()), ctypes.byref(cnt), sp))
     mma_rate = cnt.value / (mma_ms * 1e-3)
@@ -458,12 +473,14 @@ def floors_leg(w, device, stream):
         "corner_rows": n,
         "gather_rows_ms": gat_ms, "gather_rows_per_s": n / (gat_ms * 1e-3),
         "red_f16x2_rows_ms": red_ms, "red_f16x2_rows_per_s": n / (red_ms * 1e-3),
+        "gather_red_rows_ms": both_ms, "gather_red_idle_smem_bytes_per_cta": bwd_smem,
         "red_f16x2_rows_per_s_by_issuing_sms": red_by_sms,
         "bulk_reduce_f16_rows_per_s_by_piece_bytes": bulk_by_piece,
         "mma_m16n8k16_per_s": mma_rate,
         "smem_row_updates_per_s": rmw_rate,
         "reading": "a forward cannot finish before gather_rows_ms; a backward that adds every "
-                   "corner row into global memory cannot finish before red_f16x2_rows_ms; the "
+                   "corner row into global memory cannot finish before red_f16x2_rows_ms, nor, as it must "
+                   "gather the same rows first, before gather_red_rows_ms; the "
                    "reduction rate falls in proportion to the SMs that issue, so the limit is each "
                    "SM's path to L2 (one 64-byte row in about four cycles), not L2's reduction units; "
                    "the copy engine's bulk reductions leave the SM no faster",

@@ -15,6 +15,11 @@
 //                       the other way out of the SM is any wider)
 //   floors_gather_rows  one 16-byte read-only load per lane; four lanes cover a row
 //                       (what the forward's and backward's corner gather costs in L1 / L2)
+//   floors_gather_red_rows  both: every lane loads its 16 bytes of a row of `src` and adds 16
+//                       bytes into the same row of `dst`, eight rows in flight per lane, with
+//                       as much idle shared memory per CTA as the caller says (the backward
+//                       kernel's, so that L1 keeps the capacity it has there) - the backward
+//                       kernel minus its arithmetic, descriptors and gradient write-out
 //   floors_mma          back-to-back mma.sync m16n8k16 bf16 instructions, eight independent
 //                       accumulator sets per warp (legacy tensor-core issue rate of one SM)
 //   floors_smem_rmw     16-byte load / packed add / store on warp-private shared memory rows
@@ -93,6 +98,39 @@ __global__ void __launch_bounds__(kThreads) gather_rows_kernel(const uint16_t *s
         acc ^= v.x ^ v.y ^ v.z ^ v.w;
     }
     if (acc == 0x9e3779b9u) *sink = acc;   // keeps the loads alive; practically never taken
+}
+
+__global__ void __launch_bounds__(kThreads, 4) gather_red_rows_kernel(const uint16_t *src, uint16_t *dst,
+                                                                    const uint32_t *row_off, int64_t rows) {
+    constexpr int kInFlight = 8;
+    const int sub = threadIdx.x & 3;
+    const int64_t stride = (int64_t)gridDim.x * (kThreads / 4);
+    for (int64_t r = (int64_t)blockIdx.x * (kThreads / 4) + (threadIdx.x >> 2); r < rows;
+         r += kInFlight * stride) {
+        uint32_t off[kInFlight];
+        uint4 v[kInFlight];
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u)
+            off[u] = r + u * stride < rows ? row_off[r + u * stride] : 0xffffffffu;
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+            v[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (off[u] != 0xffffffffu)
+                asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                             : "l"(src + off[u] + sub * 8));
+        }
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+            if (off[u] == 0xffffffffu) continue;
+            // an addend that depends on what was loaded, and stays small whatever that was
+            const uint32_t a = ((v[u].x ^ v[u].y ^ v[u].z ^ v[u].w) & 0x03ff03ffu) | 0x10001000u;
+            asm volatile("red.relaxed.gpu.global.add.noftz.v4.f16x2 [%0], {%1, %1, %1, %1};" ::"l"(
+                             dst + off[u] + sub * 8),
+                         "r"(a)
+                         : "memory");
+        }
+    }
 }
 
 __global__ void __launch_bounds__(kThreads) mma_kernel(int iters, float *sink) {
@@ -196,6 +234,16 @@ int floors_gather_rows(const void *src, const uint32_t *row_off, int64_t rows, v
                        void *stream) {
     gather_rows_kernel<<<grid_for(8), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t *>(src), row_off, rows, static_cast<uint32_t *>(sink));
+    return (int)cudaGetLastError();
+}
+
+// idle_smem_bytes: dynamic shared memory each CTA holds without using it (four CTAs per SM)
+int floors_gather_red_rows(const void *src, void *dst, const uint32_t *row_off, int64_t rows,
+                           int idle_smem_bytes, void *stream) {
+    if (idle_smem_bytes < 0 || idle_smem_bytes > 48 * 1024) return (int)cudaErrorInvalidValue;
+    gather_red_rows_kernel<<<grid_for(4), kThreads, (size_t)idle_smem_bytes,
+                             static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t *>(src), static_cast<uint16_t *>(dst), row_off, rows);
     return (int)cudaGetLastError();
 }
 

@@ -39,6 +39,15 @@
 // Measured on B200 at the headline shape (backward call, ms, with an earlier accumulation scheme
 // whose extra passes cost 0.04 ms more than today's; the order is what matters): unroll 2 / 4
 // CTAs 0.583, 3 / 4 0.585, 1 / 4 0.593, 1 / 3 0.604, 2 / 3 0.605, 4 / 4 0.680, 1 / 5 0.815.
+#ifndef MSDA_PREP_CTAS_PER_SM
+#define MSDA_PREP_CTAS_PER_SM 16
+#endif
+#ifndef MSDA_FIN_CTAS_PER_SM
+#define MSDA_FIN_CTAS_PER_SM 16
+#endif
+#ifndef MSDA_FIN_VECS
+#define MSDA_FIN_VECS 4
+#endif
 #ifndef MSDA_BWD_UNROLL
 #define MSDA_BWD_UNROLL 2
 #endif
@@ -84,6 +93,10 @@ __global__ void __launch_bounds__(256, MSDA_BWD_MIN_CTAS) backward_kernel(const 
 
     load_level_table(lt, p);
     __syncthreads();
+    // everything above reads the caller's tables only; the scratch header and image below are
+    // written by the kernel before this one
+    grid_dependency_wait();
+    grid_launch_dependents();
     float scale = 1.f;
     if constexpr (SCALED) {
         scale = ldexpf(1.f, grad_scale_exponent<T>(reinterpret_cast<const unsigned *>(p.scratch),
@@ -312,6 +325,7 @@ __device__ __forceinline__ unsigned scan_max_magnitude(const uint4 *__restrict__
 // zero on the stream before this kernel.
 template <bool WITH_ATTN>
 __global__ void __launch_bounds__(256) prepare_kernel(const Params p) {
+    grid_launch_dependents();   // the backward kernel may load its tables meanwhile
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     unsigned *header = reinterpret_cast<unsigned *>(p.scratch);
@@ -333,12 +347,20 @@ __global__ void __launch_bounds__(256) prepare_kernel(const Params p) {
         const unsigned short *tail = reinterpret_cast<const unsigned short *>(p.attn);
         for (int64_t i = (n / 8) * 8 + first; i < n; i += stride) ma = max(ma, tail[i] & 0x7fffu);
     }
+    // one atomic per CTA and cell: the warps' maxima meet in shared memory first (every warp
+    // finishes at about the same time, and same-address atomics are served one after another)
+    __shared__ unsigned cta_max[2];
+    if (threadIdx.x < 2) cta_max[threadIdx.x] = 0u;
+    __syncthreads();
     mg = __reduce_max_sync(0xffffffffu, mg);
-    if ((threadIdx.x & 31) == 0 && mg != 0) atomicMax(header, mg);
-    if constexpr (WITH_ATTN) {
-        ma = __reduce_max_sync(0xffffffffu, ma);
-        if ((threadIdx.x & 31) == 0 && ma != 0) atomicMax(header + 1, ma);
+    if constexpr (WITH_ATTN) ma = __reduce_max_sync(0xffffffffu, ma);
+    if ((threadIdx.x & 31) == 0) {
+        if (mg != 0) atomicMax(&cta_max[0], mg);
+        if (WITH_ATTN && ma != 0) atomicMax(&cta_max[1], ma);
     }
+    __syncthreads();
+    if (threadIdx.x < (WITH_ATTN ? 2 : 1) && cta_max[threadIdx.x] != 0)
+        atomicMax(header + threadIdx.x, cta_max[threadIdx.x]);
 }
 
 // grad_value = (image + the replicas of the position's level) * 2^-e, rounded to T
@@ -350,6 +372,7 @@ __global__ void __launch_bounds__(256) finalize_kernel(const Params p) {
     __syncthreads();
     if (threadIdx.x == 0) plan_replicas(lt, p);
     __syncthreads();
+    grid_dependency_wait();     // the image is complete once the backward kernel has finished
     bool any_extra = false;
     for (int l = 0; l < p.L; ++l) any_extra |= lt.rep[l] > 1;
     const int GD = p.G * p.D;
@@ -362,30 +385,36 @@ __global__ void __launch_bounds__(256) finalize_kernel(const Params p) {
                                                          kScratchHeaderBytes);
     const int64_t total = p.B * p.S * (p.G * p.D / 8);
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t v0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v0 < total; v0 += 4 * stride) {
-      // four vectors per turn, their image loads issued together
-      uint4 raw[4];
+    const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    // where the thread's current vector lies - sample b, pixel s of the sample, vector col of the
+    // pixel's row - kept up to date by additions: one division per thread instead of two per vector
+    const int64_t first_row = first / vec_per_row;
+    int col = (int)(first - first_row * vec_per_row);
+    int64_t b = p.S > 0 ? first_row / p.S : 0;
+    int64_t s = first_row - b * p.S;
+    const int64_t step_rows = stride / vec_per_row;
+    const int step_cols = (int)(stride - step_rows * vec_per_row);
+    constexpr int kTurn = MSDA_FIN_VECS;
+    for (int64_t v0 = first; v0 < total; v0 += kTurn * stride) {
+      // several vectors per turn, their image loads issued together
+      uint4 raw[kTurn];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < kTurn; ++u)
           raw[u] = v0 + u * stride < total ? ld_stream16(image + v0 + u * stride) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < kTurn; ++u) {
         const int64_t v = v0 + u * stride;
         if (v >= total) break;
         float2 f[4];
         VecTraits<__half>::unpack(raw[u], f);
         if (any_extra) {
-            const int64_t row = v / vec_per_row;
-            const int64_t b = row / p.S;
-            const int s = (int)(row - b * p.S);
             const __half *sample_extras = reinterpret_cast<const __half *>(image) +
-                                          p.B * p.S * (int64_t)GD + b * extra_sample +
-                                          (v - row * vec_per_row) * 8;
+                                          p.B * p.S * (int64_t)GD + b * extra_sample + col * 8;
             // every level whose pixel range holds this position (one, for a well-formed table)
             for (int l = 0; l < p.L; ++l) {
-                const int at = s - lt.start[l];
-                if (lt.rep[l] <= 1 || at < 0 || at >= lt.H[l] * lt.W[l]) continue;
-                const __half *src = sample_extras + lt.rep_base[l] + (int64_t)at * GD;
+                const int64_t at = s - lt.start[l];
+                if (lt.rep[l] <= 1 || at < 0 || at >= (int64_t)lt.H[l] * lt.W[l]) continue;
+                const __half *src = sample_extras + lt.rep_base[l] + at * GD;
                 for (int r = 1; r < lt.rep[l]; ++r) {
                     float2 x[4];
                     VecTraits<__half>::unpack(
@@ -396,6 +425,17 @@ __global__ void __launch_bounds__(256) finalize_kernel(const Params p) {
                         f[i].y += x[i].y;
                     }
                 }
+            }
+            // on to the vector one stride further
+            col += step_cols;
+            s += step_rows;
+            if (col >= vec_per_row) {
+                col -= vec_per_row;
+                ++s;
+            }
+            while (s >= p.S) {
+                s -= p.S;
+                ++b;
             }
         }
 #pragma unroll
@@ -429,6 +469,7 @@ cudaError_t launch_kernel(const Params &p, cudaStream_t stream) {
     const int64_t ctas = (p.num_groups + per_cta - 1) / per_cta;
     if (ctas > 0x7fffffffll) return cudaErrorInvalidConfiguration;   // > 10^11 pairs
     q.grid = (unsigned)ctas;
+    if constexpr (SCALED) return launch_after_predecessor(kernel, q.grid, q.threads, smem, stream, q);
     kernel<<<q.grid, q.threads, smem, stream>>>(q);
     return cudaGetLastError();
 }
@@ -441,10 +482,11 @@ cudaError_t launch_typed(const Params &p, cudaStream_t stream) {
     return launch_kernel<T, SOFTMAX, false>(p, stream);
 }
 
-unsigned sweep_grid(const Params &p, int vec) {
+unsigned sweep_grid(const Params &p, int vec, int ctas_per_sm) {
     const int64_t total = p.B * p.S * (p.G * p.D / vec);
     const int64_t blocks = (total + 256 * 4 - 1) / (256 * 4);   // ~4 vectors per thread
-    return (unsigned)(blocks < 1 ? 1 : (blocks > 148 * 16 ? 148 * 16 : blocks));
+    const int64_t cap = 148 * (int64_t)ctas_per_sm;
+    return (unsigned)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 
 }  // namespace
@@ -475,24 +517,22 @@ cudaError_t launch_prepare_grad_value(const Params &p, int dtype, bool softmax, 
     cudaError_t e = cudaMemsetAsync(p.scratch, 0, kScratchHeaderBytes, stream);
     if (e != cudaSuccess) return e;
     if (softmax)
-        prepare_kernel<false><<<sweep_grid(p, 8), 256, 0, stream>>>(p);
+        prepare_kernel<false><<<sweep_grid(p, 8, MSDA_PREP_CTAS_PER_SM), 256, 0, stream>>>(p);
     else
-        prepare_kernel<true><<<sweep_grid(p, 8), 256, 0, stream>>>(p);
+        prepare_kernel<true><<<sweep_grid(p, 8, MSDA_PREP_CTAS_PER_SM), 256, 0, stream>>>(p);
     return cudaGetLastError();
 }
 
 cudaError_t launch_finalize_grad_value(const Params &p, int dtype, bool softmax, cudaStream_t stream) {
-    const unsigned grid = sweep_grid(p, 8);
-    if (dtype == 1) {
-        if (softmax) finalize_kernel<__half, true><<<grid, 256, 0, stream>>>(p);
-        else finalize_kernel<__half, false><<<grid, 256, 0, stream>>>(p);
-    } else if (dtype == 2) {
-        if (softmax) finalize_kernel<__nv_bfloat16, true><<<grid, 256, 0, stream>>>(p);
-        else finalize_kernel<__nv_bfloat16, false><<<grid, 256, 0, stream>>>(p);
-    } else {
-        return cudaErrorInvalidValue;
-    }
-    return cudaGetLastError();
+    const unsigned grid = sweep_grid(p, 8, MSDA_FIN_CTAS_PER_SM);
+    if (dtype == 1)
+        return softmax ? launch_after_predecessor(finalize_kernel<__half, true>, grid, 256, 0, stream, p)
+                       : launch_after_predecessor(finalize_kernel<__half, false>, grid, 256, 0, stream, p);
+    if (dtype == 2)
+        return softmax
+                   ? launch_after_predecessor(finalize_kernel<__nv_bfloat16, true>, grid, 256, 0, stream, p)
+                   : launch_after_predecessor(finalize_kernel<__nv_bfloat16, false>, grid, 256, 0, stream, p);
+    return cudaErrorInvalidValue;
 }
 
 }  // namespace msda_b200
