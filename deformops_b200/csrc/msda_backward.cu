@@ -32,13 +32,20 @@
 
 // What bounds this kernel on B200 is not arithmetic and not DRAM but each SM's request path to
 // L2, which the gather's L1 misses share with the reductions: a kernel that issues nothing but
-// this kernel's reductions takes 0.41 ms at the headline shape (csrc/floors/bench_floors.cu),
-// this one 0.48 ms.
+// this kernel's reductions takes 0.40 ms at the headline shape, one that gathers every row and
+// then adds into it 0.47 ms (csrc/floors/bench_floors.cu), this one 0.47 ms.
 //
 // tuning knobs (compile-time): points in flight together and CTAs per SM the registers allow.
 // Measured on B200 at the headline shape (backward call, ms, with an earlier accumulation scheme
 // whose extra passes cost 0.04 ms more than today's; the order is what matters): unroll 2 / 4
 // CTAs 0.583, 3 / 4 0.585, 1 / 4 0.593, 1 / 3 0.604, 2 / 3 0.605, 4 / 4 0.680, 1 / 5 0.815.
+//
+// The two sweep kernels around the backward kernel (prepare, finalize): CTAs of the grid per SM,
+// vectors a finalize thread has in flight, and the residency the register allocation is held
+// to.  Measured on B200 at the headline shape (backward call, ms): grid and vectors are flat
+// (8..32 CTAs per SM, 2..8 vectors: 0.529-0.537); registers are not - prepare left alone takes
+// 87 registers and costs 0.014 ms more than at 56, held to 32 it gains another 0.002; finalize
+// held to 64 registers gains 0.004 over 72 (0.5250 -> 0.5192 together).
 #ifndef MSDA_PREP_CTAS_PER_SM
 #define MSDA_PREP_CTAS_PER_SM 16
 #endif
@@ -47,6 +54,12 @@
 #endif
 #ifndef MSDA_FIN_VECS
 #define MSDA_FIN_VECS 4
+#endif
+#ifndef MSDA_FIN_MIN_CTAS
+#define MSDA_FIN_MIN_CTAS 4
+#endif
+#ifndef MSDA_PREP_MIN_CTAS
+#define MSDA_PREP_MIN_CTAS 8
 #endif
 #ifndef MSDA_BWD_UNROLL
 #define MSDA_BWD_UNROLL 2
@@ -324,7 +337,7 @@ __device__ __forceinline__ unsigned scan_max_magnitude(const uint4 *__restrict__
 // (and, without softmax, |attn|) element in the scratch header.  The header cells were set to
 // zero on the stream before this kernel.
 template <bool WITH_ATTN>
-__global__ void __launch_bounds__(256) prepare_kernel(const Params p) {
+__global__ void __launch_bounds__(256, MSDA_PREP_MIN_CTAS) prepare_kernel(const Params p) {
     grid_launch_dependents();   // the backward kernel may load its tables meanwhile
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -363,85 +376,106 @@ __global__ void __launch_bounds__(256) prepare_kernel(const Params p) {
         atomicMax(header + threadIdx.x, cta_max[threadIdx.x]);
 }
 
-// grad_value = (image + the replicas of the position's level) * 2^-e, rounded to T
+// grad_value = (image + the replicas of the position's level) * 2^-e, rounded to T.
+// Positions of levels that have replicas form a small range of every sample (the coarse levels:
+// 1 024 of 21 504 positions at the headline shape); everything outside it takes the short path.
 template <typename T, bool SOFTMAX>
-__global__ void __launch_bounds__(256) finalize_kernel(const Params p) {
+__global__ void __launch_bounds__(256, MSDA_FIN_MIN_CTAS) finalize_kernel(const Params p) {
     using VT = VecTraits<T>;
     __shared__ LevelTable lt;
+    __shared__ int extra_range[2];
     load_level_table(lt, p);
     __syncthreads();
-    if (threadIdx.x == 0) plan_replicas(lt, p);
+    if (threadIdx.x == 0) {
+        plan_replicas(lt, p);
+        int lo = 0x7fffffff, hi = 0;
+        for (int l = 0; l < p.L; ++l)
+            if (lt.rep[l] > 1) {
+                lo = min(lo, lt.start[l]);
+                hi = max(hi, lt.start[l] + lt.H[l] * lt.W[l]);
+            }
+        extra_range[0] = lo;
+        extra_range[1] = hi;
+    }
     __syncthreads();
     grid_dependency_wait();     // the image is complete once the backward kernel has finished
-    bool any_extra = false;
-    for (int l = 0; l < p.L; ++l) any_extra |= lt.rep[l] > 1;
+    const int extra_lo = extra_range[0], extra_hi = extra_range[1];
+    const bool any_extra = extra_lo < extra_hi;
     const int GD = p.G * p.D;
     const int vec_per_row = GD / 8;
+    const int S = (int)p.S;
     const int64_t extra_sample = extra_elems_per_sample(p.Q, p.G, p.D, p.L, p.K);
     const float inv = ldexpf(1.f, -grad_scale_exponent<T>(reinterpret_cast<const unsigned *>(p.scratch),
                                                           p.Q, p.K, SOFTMAX));
     const float2 inv2 = make_float2(inv, inv);
     const uint4 *image = reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(p.scratch) +
                                                          kScratchHeaderBytes);
-    const int64_t total = p.B * p.S * (p.G * p.D / 8);
+    const __half *extras = reinterpret_cast<const __half *>(image) + p.B * p.S * (int64_t)GD;
+    uint4 *gv = reinterpret_cast<uint4 *>(p.grad_value);
+    const int64_t total = p.B * p.S * (int64_t)vec_per_row;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    // where the thread's current vector lies - sample b, pixel s of the sample, vector col of the
-    // pixel's row - kept up to date by additions: one division per thread instead of two per vector
+    // where the thread's current vector lies - sample b, position s of the sample, vector col of
+    // the position's row - kept up to date by additions: one division per thread, none per vector
     const int64_t first_row = first / vec_per_row;
     int col = (int)(first - first_row * vec_per_row);
-    int64_t b = p.S > 0 ? first_row / p.S : 0;
-    int64_t s = first_row - b * p.S;
-    const int64_t step_rows = stride / vec_per_row;
-    const int step_cols = (int)(stride - step_rows * vec_per_row);
+    int64_t b = first_row / S;
+    int s = (int)(first_row - b * S);
+    const int64_t step_rows64 = stride / vec_per_row;
+    const int step_cols = (int)(stride - step_rows64 * vec_per_row);
+    const int step_samples = (int)(step_rows64 / S);          // whole samples per stride
+    const int step_rows = (int)(step_rows64 - (int64_t)step_samples * S);
     constexpr int kTurn = MSDA_FIN_VECS;
     for (int64_t v0 = first; v0 < total; v0 += kTurn * stride) {
-      // several vectors per turn, their image loads issued together
-      uint4 raw[kTurn];
+        // several vectors per turn, their image loads issued together
+        uint4 raw[kTurn];
 #pragma unroll
-      for (int u = 0; u < kTurn; ++u)
-          raw[u] = v0 + u * stride < total ? ld_stream16(image + v0 + u * stride) : make_uint4(0u, 0u, 0u, 0u);
+        for (int u = 0; u < kTurn; ++u)
+            raw[u] = v0 + u * stride < total ? ld_stream16(image + v0 + u * stride)
+                                             : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-      for (int u = 0; u < kTurn; ++u) {
-        const int64_t v = v0 + u * stride;
-        if (v >= total) break;
-        float2 f[4];
-        VecTraits<__half>::unpack(raw[u], f);
-        if (any_extra) {
-            const __half *sample_extras = reinterpret_cast<const __half *>(image) +
-                                          p.B * p.S * (int64_t)GD + b * extra_sample + col * 8;
-            // every level whose pixel range holds this position (one, for a well-formed table)
-            for (int l = 0; l < p.L; ++l) {
-                const int64_t at = s - lt.start[l];
-                if (lt.rep[l] <= 1 || at < 0 || at >= (int64_t)lt.H[l] * lt.W[l]) continue;
-                const __half *src = sample_extras + lt.rep_base[l] + at * GD;
-                for (int r = 1; r < lt.rep[l]; ++r) {
-                    float2 x[4];
-                    VecTraits<__half>::unpack(
-                        ld_stream16(src + (int64_t)(r - 1) * lt.level_elems[l]), x);
+        for (int u = 0; u < kTurn; ++u) {
+            const int64_t v = v0 + u * stride;
+            if (v >= total) break;
+            float2 f[4];
+            VecTraits<__half>::unpack(raw[u], f);
+            if (any_extra) {
+                if (s >= extra_lo && s < extra_hi) {
+                    const __half *sample_extras = extras + b * extra_sample + col * 8;
+                    // every level whose range holds this position (one, for a well-formed table)
+                    for (int l = 0; l < p.L; ++l) {
+                        const int at = s - lt.start[l];
+                        if (lt.rep[l] <= 1 || at < 0 || at >= lt.H[l] * lt.W[l]) continue;
+                        const __half *src = sample_extras + lt.rep_base[l] + (int64_t)at * GD;
+                        for (int r = 1; r < lt.rep[l]; ++r) {
+                            float2 x[4];
+                            VecTraits<__half>::unpack(
+                                ld_stream16(src + (int64_t)(r - 1) * lt.level_elems[l]), x);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        f[i].x += x[i].x;
-                        f[i].y += x[i].y;
+                            for (int i = 0; i < 4; ++i) {
+                                f[i].x += x[i].x;
+                                f[i].y += x[i].y;
+                            }
+                        }
                     }
                 }
+                // on to the vector one stride further
+                col += step_cols;
+                s += step_rows;
+                b += step_samples;
+                if (col >= vec_per_row) {
+                    col -= vec_per_row;
+                    ++s;
+                }
+                if (s >= S) {
+                    s -= S;
+                    ++b;
+                }
             }
-            // on to the vector one stride further
-            col += step_cols;
-            s += step_rows;
-            if (col >= vec_per_row) {
-                col -= vec_per_row;
-                ++s;
-            }
-            while (s >= p.S) {
-                s -= p.S;
-                ++b;
-            }
-        }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) f[i] = fmul2(f[i], inv2);
-        reinterpret_cast<uint4 *>(p.grad_value)[v] = VT::pack(f);
-      }
+            for (int i = 0; i < 4; ++i) f[i] = fmul2(f[i], inv2);
+            gv[v] = VT::pack(f);
+        }
     }
 }
 
