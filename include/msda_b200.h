@@ -93,7 +93,10 @@ int msda_b200_forward(const void *value, const int64_t *spatial_shapes,
  * largest |grad_out| and |attn| element so that no sum can leave the float16 range, adds it
  * in float16 (11 significant bits, packed 16-byte reductions) into an image of grad_value
  * held in the scratch (a level that receives more than 256 additions per element is given
- * several accumulators there), and a last pass unscales the sums into grad_value in `dtype`.  With
+ * several accumulators there), and a last pass unscales the sums into grad_value in `dtype`.  Such
+ * a call enqueues a 256-byte memset and three kernels; for large shapes the second and third are
+ * launched as programmatic dependents of the one before (they become resident while it drains
+ * and wait for its completion on the device), which CUDA-graph capture records as well.  With
  * scratch == NULL every contribution is added straight into grad_value in `dtype` (least
  * accurate for bf16).  Ignored for float32.  `scratch_adds` is accepted for callers written
  * against ABI version 4 and has no effect.

@@ -217,6 +217,45 @@ def test_forward_and_backward_replay_from_a_cuda_graph():
     torch.testing.assert_close(grads[0], e_grads[0], rtol=2e-2, atol=2e-2)
 
 
+def test_large_call_replays_from_a_cuda_graph():
+    """A backward call long enough to launch its second and third kernel as programmatic
+    dependents of the one before (2^21 (query, head, point) triples and up) is captured and
+    replayed like any other: the replay on new data equals an ordinary call on that data."""
+    from deformops_b200.registry import msda
+    from deformops_b200.workloads import make_workload
+
+    w = make_workload("cfg2_m2f_1024_bf16", batch=2).to("cuda")
+    B, S, G, D, Q, L, K = w.dims
+    assert B * Q * G * L * K >= 1 << 21
+    value = w.value.clone().requires_grad_(True)
+    loc = w.sampling_locations.clone().requires_grad_(True)
+    attn = w.attention_weights.clone().requires_grad_(True)
+
+    def step():
+        out = msda(value, w.spatial_shapes, w.level_start_index, loc, attn)
+        return out, torch.autograd.grad(out, [value, loc, attn], w.grad_output)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out, grads = step()
+    with torch.no_grad():
+        value.mul_(0.5)
+        loc.add_(0.003)
+    for _ in range(3):                      # several replays: the dependency edges hold every time
+        graph.replay()
+    torch.cuda.synchronize()
+    e_out, e_grads = step()
+    assert torch.equal(out, e_out)
+    assert torch.equal(grads[1], e_grads[1]) and torch.equal(grads[2], e_grads[2])
+    torch.testing.assert_close(grads[0].float(), e_grads[0].float(), rtol=2e-2, atol=2e-2)
+
+
 def test_export_and_dynamo_record_the_public_op():
     """torch.export keeps the public op in the graph and decomposes it to the private forward op;
     Dynamo traces the functional without a graph break (dynamic query count included)."""
