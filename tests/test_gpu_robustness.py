@@ -254,6 +254,27 @@ def test_levels_listed_out_of_order_bf16_with_scratch():
     assert torch.equal(other[2].view(2, 150, 8, L, K), base[2].view(2, 150, 8, L, K)[:, :, :, perm])
 
 
+@pytest.mark.parametrize("G,D", [(1, 8), (2, 24)])
+def test_many_small_samples_with_replicated_levels(G, D):
+    """Hundreds of samples of a tiny pyramid whose levels all need several accumulators: the
+    pass that folds the replicas into grad_value then strides over whole samples between the
+    vectors one thread handles, and its running (sample, position, column) must stay right."""
+    B, Q, K = 600, 300, 4
+    value, shapes, starts, loc, logits, grad_out = _case(11, B, Q, G, D, K, [(4, 4), (2, 2)], spread=1.1)
+    attn = logits.softmax(-1)
+    dt = torch.bfloat16
+    v, a, go = dev(value, dt), dev(attn, dt), dev(grad_out, dt)
+    gv, gl, ga = abi_backward(v, dev(shapes), dev(starts), dev(loc, torch.float32), a, go)
+    t_gv, t_gl, t_ga = orc.backward(v.cpu(), shapes, starts, loc, a.cpu(), go.cpu())
+    assert rel_err(to_np(gv), t_gv) <= 1e-2
+    assert rel_err(to_np(gl), t_gl) <= 1e-2 and rel_err(to_np(ga), t_ga) <= 1e-2
+    # sample by sample as well: an error confined to a few samples would vanish in the global norm
+    g = to_np(gv).reshape(B, -1)
+    t = np.asarray(t_gv).reshape(B, -1)
+    worst = np.max(np.abs(g - t), axis=1) / (np.max(np.abs(t), axis=1) + 1e-30)
+    assert worst.max() <= 2e-2, (int(worst.argmax()), float(worst.max()))
+
+
 @pytest.mark.parametrize("dtype,exponent", [
     (torch.bfloat16, -14), (torch.bfloat16, 0), (torch.bfloat16, 12),
     # (float16 itself ends at 65504: at 2^12 the true grad_attn no longer fits the dtype)
