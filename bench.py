@@ -22,9 +22,11 @@ Legs, all inside one run:
                the same way (max over ranks); every rank also checks the results on its own
                slice against the reference's CUDA kernel (or the C oracle on one sample when
                that library was not built) and the run fails if a tolerance is exceeded.
-  floors       N=1: what kernels that only gather rows / only issue reductions / only issue
-               tensor-core instructions reach on the operator's own addresses (bench-only
-               library, not part of libmsda_b200.so).
+  floors       N=1: what kernels reach that only gather the operator's rows, only add into them
+               (packed reductions, and the copy engine's bulk reductions), or do both and
+               nothing else, on the operator's own addresses; plus the issue rates of
+               tensor-core instructions and shared-memory row updates (bench-only library,
+               not part of libmsda_b200.so).
   gpu_baseline N=1: the reference's own GPU implementations on this GPU and these inputs - its
                CUDA kernels (production float32-accumulate and 16-bit-atomics builds) and its
                Triton backend - with peak memory beside ours.
