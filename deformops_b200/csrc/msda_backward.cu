@@ -42,15 +42,17 @@
 //
 // The two sweep kernels around the backward kernel (prepare, finalize): CTAs of the grid per SM,
 // vectors a finalize thread has in flight, and the residency the register allocation is held
-// to.  Measured on B200 at the headline shape (backward call, ms): grid and vectors are flat
-// (8..32 CTAs per SM, 2..8 vectors: 0.529-0.537); registers are not - prepare left alone takes
-// 87 registers and costs 0.014 ms more than at 56, held to 32 it gains another 0.002; finalize
-// held to 64 registers gains 0.004 over 72 (0.5250 -> 0.5192 together).
+// to.  Measured on B200 at the headline shape (backward call, ms): prepare's grid and finalize's
+// vectors are flat (8..32 CTAs per SM, 2..8 vectors); registers are not - prepare left alone
+// takes 87 registers and costs 0.014 ms more than at 56, held to 32 it gains another 0.002;
+// finalize held to 64 registers gains 0.004 over 72 (0.5250 -> 0.5192 together) - and finalize
+// wants exactly the CTAs that fit at once: one wave of four per SM 0.5138, three 0.5169, sixteen
+// (two waves, each thread paying its set-up for a quarter of the vectors) 0.5181.
 #ifndef MSDA_PREP_CTAS_PER_SM
 #define MSDA_PREP_CTAS_PER_SM 16
 #endif
 #ifndef MSDA_FIN_CTAS_PER_SM
-#define MSDA_FIN_CTAS_PER_SM 16
+#define MSDA_FIN_CTAS_PER_SM 4
 #endif
 #ifndef MSDA_FIN_VECS
 #define MSDA_FIN_VECS 4
@@ -417,14 +419,15 @@ __global__ void __launch_bounds__(256, MSDA_FIN_MIN_CTAS) finalize_kernel(const 
     const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     // where the thread's current vector lies - sample b, position s of the sample, vector col of
     // the position's row - kept up to date by additions: one division per thread, none per vector
-    const int64_t first_row = first / vec_per_row;
-    int col = (int)(first - first_row * vec_per_row);
-    int64_t b = first_row / S;
-    int s = (int)(first_row - b * S);
-    const int64_t step_rows64 = stride / vec_per_row;
-    const int step_cols = (int)(stride - step_rows64 * vec_per_row);
-    const int step_samples = (int)(step_rows64 / S);          // whole samples per stride
-    const int step_rows = (int)(step_rows64 - (int64_t)step_samples * S);
+    // (first and stride are below 2^31: the grid is capped at a few thousand CTAs of 256 threads)
+    const unsigned first_row = (unsigned)first / (unsigned)vec_per_row;
+    int col = (int)((unsigned)first - first_row * (unsigned)vec_per_row);
+    int64_t b = first_row / (unsigned)S;
+    int s = (int)(first_row - (unsigned)b * (unsigned)S);
+    const unsigned step_rows_all = (unsigned)stride / (unsigned)vec_per_row;
+    const int step_cols = (int)((unsigned)stride - step_rows_all * (unsigned)vec_per_row);
+    const int step_samples = (int)(step_rows_all / (unsigned)S);          // whole samples per stride
+    const int step_rows = (int)(step_rows_all - (unsigned)step_samples * (unsigned)S);
     constexpr int kTurn = MSDA_FIN_VECS;
     for (int64_t v0 = first; v0 < total; v0 += kTurn * stride) {
         // several vectors per turn, their image loads issued together
