@@ -406,7 +406,7 @@ def floors_leg(w, device, stream):
     lib.floors_red_rows_on.argtypes = [vp, vp, i64, ctypes.c_int, vp]
     lib.floors_bulk_red_rows.argtypes = [vp, vp, i64, ctypes.c_int, vp]
     lib.floors_gather_rows.argtypes = [vp, vp, i64, vp, vp]
-    lib.floors_gather_red_rows.argtypes = [vp, vp, vp, i64, ctypes.c_int, vp]
+    lib.floors_gather_red_rows.argtypes = [vp, vp, vp, i64, ctypes.c_int, ctypes.c_int, vp]
     lib.floors_mma.argtypes = [ctypes.c_int, vp, ctypes.POINTER(i64), vp]
     lib.floors_smem_rmw.argtypes = [ctypes.c_int, ctypes.c_int, vp, ctypes.POINTER(i64), vp]
     B, S, G, D, Q, L, K = w.dims
@@ -458,11 +458,13 @@ def floors_leg(w, device, stream):
                                       smem_f, smem_b) != 0:
         raise RuntimeError("launch geometry refused the workload's shape")
     bwd_smem = min(int(smem_b.value), 48 * 1024)
+    # rows of one query on average, rounded up to whole instructions of eight rows
+    block_rows = (-(-n // (B * Q)) + 7) // 8 * 8
     if lib.floors_gather_red_rows(vp(src.data_ptr()), vp(dst.data_ptr()), vp(rows.data_ptr()), n,
-                                  bwd_smem, sp) != 0:
+                                  block_rows, bwd_smem, sp) != 0:
         raise RuntimeError("floors_gather_red_rows refused its arguments")
     both_ms = median_ms(lambda: lib.floors_gather_red_rows(vp(src.data_ptr()), vp(dst.data_ptr()),
-                                                           vp(rows.data_ptr()), n, bwd_smem, sp))
+                                                           vp(rows.data_ptr()), n, block_rows, bwd_smem, sp))
     cnt = i64(0)
     mma_ms = median_ms(lambda: lib.floors_mma(2000, vp(sink.data_ptr()), ctypes.byref(cnt), sp))
     mma_rate = cnt.value / (mma_ms * 1e-3)

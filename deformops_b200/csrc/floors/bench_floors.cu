@@ -16,7 +16,8 @@
 //   floors_gather_rows  one 16-byte read-only load per lane; four lanes cover a row
 //                       (what the forward's and backward's corner gather costs in L1 / L2)
 //   floors_gather_red_rows  both: every lane loads its 16 bytes of a row of `src` and adds 16
-//                       bytes into the same row of `dst`, eight rows in flight per lane, with
+//                       bytes into the same row of `dst`, eight rows in flight per lane, the
+//                       rows dealt to CTAs and warps as the backward kernel deals its queries, with
 //                       as much idle shared memory per CTA as the caller says (the backward
 //                       kernel's, so that L1 keeps the capacity it has there) - the backward
 //                       kernel minus its arithmetic, descriptors and gradient write-out
@@ -100,35 +101,43 @@ __global__ void __launch_bounds__(kThreads) gather_rows_kernel(const uint16_t *s
     if (acc == 0x9e3779b9u) *sink = acc;   // keeps the loads alive; practically never taken
 }
 
+// The rows are walked the way the backward kernel walks its queries: the table is cut into
+// blocks of `block_rows` consecutive rows (about one query's: its points, corners and heads), a
+// CTA takes sixteen consecutive blocks, warp w of it blocks w and 8 + w, eight rows per
+// instruction and eight instructions (two points' corners) in flight.
 __global__ void __launch_bounds__(kThreads, 4) gather_red_rows_kernel(const uint16_t *src, uint16_t *dst,
-                                                                    const uint32_t *row_off, int64_t rows) {
+                                                                    const uint32_t *row_off, int64_t rows,
+                                                                    int block_rows) {
     constexpr int kInFlight = 8;
-    const int sub = threadIdx.x & 3;
-    const int64_t stride = (int64_t)gridDim.x * (kThreads / 4);
-    for (int64_t r = (int64_t)blockIdx.x * (kThreads / 4) + (threadIdx.x >> 2); r < rows;
-         r += kInFlight * stride) {
-        uint32_t off[kInFlight];
-        uint4 v[kInFlight];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, sub = lane & 3, slot = lane >> 2;
+    for (int pass = 0; pass < 2; ++pass) {
+        const int64_t base = ((int64_t)blockIdx.x * 16 + pass * 8 + w) * block_rows;
+        for (int i = 0; i < block_rows; i += 8 * kInFlight) {
+            uint32_t off[kInFlight];
+            uint4 v[kInFlight];
 #pragma unroll
-        for (int u = 0; u < kInFlight; ++u)
-            off[u] = r + u * stride < rows ? row_off[r + u * stride] : 0xffffffffu;
+            for (int u = 0; u < kInFlight; ++u) {
+                const int64_t r = base + i + u * 8 + slot;
+                off[u] = (i + u * 8 < block_rows && r < rows) ? row_off[r] : 0xffffffffu;
+            }
 #pragma unroll
-        for (int u = 0; u < kInFlight; ++u) {
-            v[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (off[u] != 0xffffffffu)
-                asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
-                             : "l"(src + off[u] + sub * 8));
-        }
+            for (int u = 0; u < kInFlight; ++u) {
+                v[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (off[u] != 0xffffffffu)
+                    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                                 : "l"(src + off[u] + sub * 8));
+            }
 #pragma unroll
-        for (int u = 0; u < kInFlight; ++u) {
-            if (off[u] == 0xffffffffu) continue;
-            // an addend that depends on what was loaded, and stays small whatever that was
-            const uint32_t a = ((v[u].x ^ v[u].y ^ v[u].z ^ v[u].w) & 0x03ff03ffu) | 0x10001000u;
-            asm volatile("red.relaxed.gpu.global.add.noftz.v4.f16x2 [%0], {%1, %1, %1, %1};" ::"l"(
-                             dst + off[u] + sub * 8),
-                         "r"(a)
-                         : "memory");
+            for (int u = 0; u < kInFlight; ++u) {
+                if (off[u] == 0xffffffffu) continue;
+                // an addend that depends on what was loaded, and stays small whatever that was
+                const uint32_t a = ((v[u].x ^ v[u].y ^ v[u].z ^ v[u].w) & 0x03ff03ffu) | 0x10001000u;
+                asm volatile("red.relaxed.gpu.global.add.noftz.v4.f16x2 [%0], {%1, %1, %1, %1};" ::"l"(
+                                 dst + off[u] + sub * 8),
+                             "r"(a)
+                             : "memory");
+            }
         }
     }
 }
@@ -237,13 +246,18 @@ int floors_gather_rows(const void *src, const uint32_t *row_off, int64_t rows, v
     return (int)cudaGetLastError();
 }
 
-// idle_smem_bytes: dynamic shared memory each CTA holds without using it (four CTAs per SM)
+// idle_smem_bytes: dynamic shared memory each CTA holds without using it; block_rows: rows of
+// one block of the table (a multiple of 8; about the rows of one query), sixteen blocks per CTA
 int floors_gather_red_rows(const void *src, void *dst, const uint32_t *row_off, int64_t rows,
-                           int idle_smem_bytes, void *stream) {
-    if (idle_smem_bytes < 0 || idle_smem_bytes > 48 * 1024) return (int)cudaErrorInvalidValue;
-    gather_red_rows_kernel<<<grid_for(4), kThreads, (size_t)idle_smem_bytes,
+                           int block_rows, int idle_smem_bytes, void *stream) {
+    if (idle_smem_bytes < 0 || idle_smem_bytes > 48 * 1024 || block_rows < 8 || block_rows % 8 != 0)
+        return (int)cudaErrorInvalidValue;
+    const int64_t per_cta = 16ll * block_rows;
+    const int64_t ctas = (rows + per_cta - 1) / per_cta;
+    if (ctas < 1 || ctas > 0x7fffffffll) return (int)cudaErrorInvalidValue;
+    gather_red_rows_kernel<<<(unsigned)ctas, kThreads, (size_t)idle_smem_bytes,
                              static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint16_t *>(src), static_cast<uint16_t *>(dst), row_off, rows);
+        static_cast<const uint16_t *>(src), static_cast<uint16_t *>(dst), row_off, rows, block_rows);
     return (int)cudaGetLastError();
 }
 

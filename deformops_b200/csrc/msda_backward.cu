@@ -33,7 +33,7 @@
 // What bounds this kernel on B200 is not arithmetic and not DRAM but each SM's request path to
 // L2, which the gather's L1 misses share with the reductions: a kernel that issues nothing but
 // this kernel's reductions takes 0.40 ms at the headline shape, one that gathers every row and
-// then adds into it 0.47 ms (csrc/floors/bench_floors.cu), this one 0.47 ms.
+// then adds into it 0.46 ms (csrc/floors/bench_floors.cu), this one 0.47 ms.
 //
 // tuning knobs (compile-time): points in flight together and CTAs per SM the registers allow.
 // Measured on B200 at the headline shape (backward call, ms, with an earlier accumulation scheme
