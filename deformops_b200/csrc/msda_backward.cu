@@ -349,7 +349,6 @@ __global__ void __launch_bounds__(256, MSDA_PREP_MIN_CTAS) prepare_kernel(const 
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     // (the extras are cleared in full: at most K*Q*G*D*L / 64 elements per sample)
     const int64_t clear_vecs = image_vecs + p.B * (extra_elems_per_sample(p.Q, p.G, p.D, p.L, p.K) / 8);
-    for (int64_t v = first; v < clear_vecs; v += stride) image[v] = zero;
     unsigned mg = 0, ma = 0;
     const int64_t go_vecs = p.B * p.Q * (p.G * p.D / 8);
     const uint4 *go = reinterpret_cast<const uint4 *>(p.grad_out);
@@ -362,6 +361,9 @@ __global__ void __launch_bounds__(256, MSDA_PREP_MIN_CTAS) prepare_kernel(const 
         const unsigned short *tail = reinterpret_cast<const unsigned short *>(p.attn);
         for (int64_t i = (n / 8) * 8 + first; i < n; i += stride) ma = max(ma, tail[i] & 0x7fffu);
     }
+    // the clearing stores come after the scan's loads were issued: they need no answer, and the
+    // loads' round trips to DRAM are the longest thing this kernel waits for
+    for (int64_t v = first; v < clear_vecs; v += stride) image[v] = zero;
     // one atomic per CTA and cell: the warps' maxima meet in shared memory first (every warp
     // finishes at about the same time, and same-address atomics are served one after another)
     __shared__ unsigned cta_max[2];
