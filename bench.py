@@ -767,7 +767,10 @@ def main():
         except Exception as exc:  # noqa: BLE001 - the floors are context, not the measurement
             floors = {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
     if world == 1 and not args.no_gpu_baseline:
-        gpu_baseline = gpu_baseline_leg(sets, abi, device, stream, max(5, min(args.steps, 20)))
+        try:
+            gpu_baseline = gpu_baseline_leg(sets, abi, device, stream, max(5, min(args.steps, 20)))
+        except Exception as exc:  # noqa: BLE001 - the baselines are context, not the measurement
+            gpu_baseline = {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
 
     # ---- max over ranks -------------------------------------------------------------------
     stats = torch.tensor([ms_total, fwd_ms, bwd_ms, e2e["ms"] if e2e else 0.0,
